@@ -1,0 +1,102 @@
+"""Build the native parts in-tree.
+
+  libfa_b200.so   CUDA kernels + C ABI (torch-free), nvcc, sm_100a only
+  fused_attn*.so  the torch extension module ``fused_attn`` (thin C++ binding over the C ABI)
+
+Run ``python -m fused_attention_b200.build [--ext]``.  Nothing is installed outside the tree.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+EXTDIR = os.path.join(HERE, "ext")
+LIB = os.path.join(LIBDIR, "libfa_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def lib_sources() -> list[str]:
+    return [os.path.join(CSRC, f) for f in ("fa_b200.cu", "fa_kernels.cuh", "fa_ptx.cuh")] + [
+        os.path.join(ROOT, "include", "fa_b200.h")]
+
+
+def build_lib(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/fa_b200.cu into lib/libfa_b200.so (cross-compiles without a GPU)."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    if not force and not _stale(LIB, lib_sources()):
+        return LIB
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-o", LIB, os.path.join(CSRC, "fa_b200.cu")]
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+def ext_path() -> str:
+    return os.path.join(EXTDIR, "fused_attn" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_ext(force: bool = False) -> str:
+    """Compile csrc/fused_attn_binding.cpp into ext/fused_attn<abi>.so with the host compiler.
+
+    The binding has no device code, so g++ is enough; it links libfa_b200.so by relative rpath.
+    """
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    build_lib()
+    os.makedirs(EXTDIR, exist_ok=True)
+    src = os.path.join(CSRC, "fused_attn_binding.cpp")
+    out = ext_path()
+    if not force and not _stale(out, [src, LIB]):
+        return out
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = ce.CUDA_HOME or "/usr/local/cuda"
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=fused_attn",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in ce.include_paths() + [os.path.join(cuda_home, "include"), sysconfig.get_paths()["include"],
+                                     os.path.join(ROOT, "include")]:
+        cmd += ["-isystem" if "torch" in inc or "cuda" in inc else "-I", inc]
+    cmd += [src, "-o", out, f"-L{torch_lib}", f"-L{LIBDIR}", "-lfa_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu",
+            "-ltorch_cuda", "-ltorch", "-ltorch_python", f"-L{os.path.join(cuda_home, 'lib64')}", "-lcudart",
+            "-Wl,-rpath,$ORIGIN/../lib", f"-Wl,-rpath,{torch_lib}"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
+def main(argv: list[str]) -> int:
+    force = "--force" in argv
+    print(build_lib(force=force, verbose="-v" in argv))
+    if "--ext" in argv:
+        print(build_ext(force=force))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

@@ -1,0 +1,378 @@
+// C-ABI launcher of the sm_100a fused attention forward (declared in include/fa_b200.h).
+// Torch-free: it needs the CUDA runtime only; the driver's cuTensorMapEncodeTiled is looked up at
+// run time, so nothing links against libcuda.
+//
+// Replaces, in the reference: launch_attention_kernel<H, C> (include/fused_attn.cuh:860-894), the
+// (head_dim, chunk_size) dispatch switch (src/fused_attn_extention.cu:72-111) and the
+// print-and-exit error helpers (include/fused_attn.cuh:17-42).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+
+#include "fa_b200.h"
+#include "fa_kernels.cuh"
+
+namespace {
+
+using fa::Params;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceCtx {
+    bool ready = false;
+    int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
+    uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count}
+    uint32_t attr_done = 0;       // bit per kernel instance whose smem attribute is set
+    // host-buffer entry point: one stream and grow-on-demand staging buffers
+    cudaStream_t host_stream = nullptr;
+    void* stage[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v y mask
+    size_t stage_bytes[5] = {0, 0, 0, 0, 0};
+};
+
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// Caller holds g_mu and has made `device` current.
+int ensure_ctx(int device, DeviceCtx** out) {
+    if (device < 0 || device >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+    DeviceCtx& c = g_ctx[device];
+    if (!c.ready) {
+        cudaDeviceProp prop;
+        cudaError_t e = cudaGetDeviceProperties(&prop, device);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.cc_major = prop.major;
+        c.cc_minor = prop.minor;
+        c.sm_count = prop.multiProcessorCount;
+        c.smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+        e = cudaMalloc(reinterpret_cast<void**>(&c.status), 2 * sizeof(uint32_t));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        e = cudaMemset(c.status, 0, 2 * sizeof(uint32_t));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.ready = true;
+    }
+    if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+            (void)cudaGetLastError();
+            return FA_B200_ERR_DRIVER;
+        }
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = &c;
+    return FA_B200_OK;
+}
+
+// 3-D map {F, L, B} over a contiguous [B, L, F] fp16 array; box = 128 rows x min(H, 64) columns.
+int make_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L, uint32_t F, uint32_t H) {
+    const uint32_t box_cols = H < 64 ? H : 64;
+    const cuuint64_t dims[3] = {F, L, B};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(F) * 2ull,
+                                   static_cast<cuuint64_t>(F) * 2ull * L};
+    const cuuint32_t box[3] = {box_cols, static_cast<cuuint32_t>(fa::kTile), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle swz = box_cols == 64   ? CU_TENSOR_MAP_SWIZZLE_128B
+                                   : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                    : CU_TENSOR_MAP_SWIZZLE_32B;
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FA_B200_OK : FA_B200_ERR_DRIVER;
+}
+
+bool is_pow2(uint32_t x) { return x != 0 && (x & (x - 1)) == 0; }
+
+int validate(const void* q, const void* k, const void* v, const void* mask, const void* y, uint32_t B,
+             uint32_t L, uint32_t F, uint32_t H, uint32_t chunk, uint32_t flags) {
+    if (!q || !k || !v || !y) return FA_B200_ERR_NULL_POINTER;
+    if (!(H == 16 || H == 32 || H == 64 || H == 128)) return FA_B200_ERR_HEAD_DIM;
+    if (chunk != 0) {
+        // the reference's rule set, src/fused_attn_extention.cu:46-47
+        if (!is_pow2(chunk) || chunk < 16 || chunk > 128 || chunk > 2 * H) return FA_B200_ERR_CHUNK;
+        if (chunk == 16 && H == 128) return FA_B200_ERR_CHUNK;
+    }
+    if (B == 0 || L == 0 || F == 0 || F % H != 0) return FA_B200_ERR_SHAPE;
+    if (B > 65535u || F / H > 65535u || L > (1u << 30)) return FA_B200_ERR_SHAPE;  // grid y/z limits
+    const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(y);
+    if (all & 15u) return FA_B200_ERR_ALIGNMENT;
+    if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return FA_B200_ERR_ALIGNMENT;
+    const uint32_t known = FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_SYNC;
+    if (flags & ~known) return FA_B200_ERR_FLAGS;
+    if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
+    if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && (mask || H < 64)) return FA_B200_ERR_FLAGS;
+    return FA_B200_OK;
+}
+
+// 1 = simple kernel, 2 = pipelined kernel.
+int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask, uint32_t flags,
+                  int sm_count) {
+    if (flags & FA_B200_FLAG_FORCE_SIMPLE) return 1;
+    if (flags & FA_B200_FLAG_FORCE_PIPELINED) return 2;
+    if (has_mask || H < 64) return 1;
+    // The pipelined kernel works on pairs of query tiles and wants one CTA per SM to have a
+    // long key loop; short sequences or too few CTAs to fill the SMs go to the simple kernel.
+    const uint64_t pairs = static_cast<uint64_t>((L + 255) / 256) * (F / H) * B;
+    if (L <= 256) return 1;
+    if (pairs < static_cast<uint64_t>(sm_count)) return 1;
+    return 2;
+}
+
+template <int H, bool M>
+int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
+                  const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+    constexpr int smem = 3 * fa::TileGeom<H>::kTileBytes + 1024;
+    auto kern = fa::fa_fwd_simple<H, M>;
+    if (!(c.attr_done & (1u << slot))) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.attr_done |= (1u << slot);
+    }
+    const dim3 grid((p.L + fa::kTile - 1) / fa::kTile, p.F / H, p.B);
+    kern<<<grid, 128, smem, st>>>(mq, mk, mv, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <int H>
+int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
+                     const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+    constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
+    auto kern = fa::fa_fwd_pipelined<H>;
+    if (!(c.attr_done & (1u << slot))) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.attr_done |= (1u << slot);
+    }
+    const dim3 grid((p.L + 2 * fa::kTile - 1) / (2 * fa::kTile), p.F / H, p.B);
+    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+// Device-pointer launch on `st`.  Caller holds no lock.
+int forward_device(const void* q, const void* k, const void* v, const void* mask, void* y, uint32_t B,
+                   uint32_t L, uint32_t F, uint32_t H, int device, cudaStream_t st, uint32_t flags) {
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device) {
+        e = cudaSetDevice(device);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    int rc = FA_B200_OK;
+    DeviceCtx* c = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        rc = ensure_ctx(device, &c);
+        if (rc == FA_B200_OK && c->cc_major != 10) rc = FA_B200_ERR_ARCH;
+        if (rc == FA_B200_OK) {
+            CUtensorMap mq, mk, mv;
+            rc = make_map(&mq, q, B, L, F, H);
+            if (rc == FA_B200_OK) rc = make_map(&mk, k, B, L, F, H);
+            if (rc == FA_B200_OK) rc = make_map(&mv, v, B, L, F, H);
+            if (rc == FA_B200_OK) {
+                Params p;
+                p.y = static_cast<__half*>(y);
+                p.mask = static_cast<const __half*>(mask);
+                p.status = c->status;
+                p.B = B;
+                p.L = L;
+                p.F = F;
+                p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
+                p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
+                p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+                const int which = select_kernel(B, L, F, H, mask != nullptr, flags, c->sm_count);
+                if (which == 2) {
+                    rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, p, st)
+                                  : launch_pipelined<64>(*c, 9, mq, mk, mv, p, st);
+                } else if (mask) {
+                    switch (H) {
+                        case 16: rc = launch_simple<16, true>(*c, 4, mq, mk, mv, p, st); break;
+                        case 32: rc = launch_simple<32, true>(*c, 5, mq, mk, mv, p, st); break;
+                        case 64: rc = launch_simple<64, true>(*c, 6, mq, mk, mv, p, st); break;
+                        default: rc = launch_simple<128, true>(*c, 7, mq, mk, mv, p, st); break;
+                    }
+                } else {
+                    switch (H) {
+                        case 16: rc = launch_simple<16, false>(*c, 0, mq, mk, mv, p, st); break;
+                        case 32: rc = launch_simple<32, false>(*c, 1, mq, mk, mv, p, st); break;
+                        case 64: rc = launch_simple<64, false>(*c, 2, mq, mk, mv, p, st); break;
+                        default: rc = launch_simple<128, false>(*c, 3, mq, mk, mv, p, st); break;
+                    }
+                }
+            }
+        }
+    }
+    if (rc == FA_B200_OK && (flags & FA_B200_FLAG_SYNC)) {
+        e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) {
+            rc = static_cast<int>(e);
+        } else {
+            uint32_t w[2] = {0, 0};
+            e = cudaMemcpy(w, c->status, sizeof(w), cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+            else if (w[0] != 0) rc = FA_B200_ERR_DEVICE_TIMEOUT;
+        }
+    }
+    if (prev != device) (void)cudaSetDevice(prev);
+    return rc;
+}
+
+int grow(DeviceCtx& c, int i, size_t bytes) {
+    if (c.stage_bytes[i] >= bytes) return FA_B200_OK;
+    if (c.stage[i]) (void)cudaFree(c.stage[i]);
+    c.stage[i] = nullptr;
+    c.stage_bytes[i] = 0;
+    cudaError_t e = cudaMalloc(&c.stage[i], bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    c.stage_bytes[i] = bytes;
+    return FA_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fa_b200_attention_forward(const void* q, const void* k, const void* v, const void* mask_or_null,
+                              void* y, uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
+                              uint32_t chunk_hint, int device, void* cuda_stream, uint32_t flags) {
+    const int rc = validate(q, k, v, mask_or_null, y, B, L, F, head_dim, chunk_hint, flags);
+    if (rc != FA_B200_OK) return rc;
+    return forward_device(q, k, v, mask_or_null, y, B, L, F, head_dim, device,
+                          static_cast<cudaStream_t>(cuda_stream), flags);
+}
+
+int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, const void* mask_or_null,
+                                   void* y, uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
+                                   uint32_t chunk_hint, int device, uint32_t flags) {
+    // Host pointers need no 16-byte alignment; validate everything else with aligned stand-ins.
+    if (!q || !k || !v || !y) return FA_B200_ERR_NULL_POINTER;
+    alignas(16) static const char aligned_dummy[16] = {0};
+    int rc = validate(aligned_dummy, aligned_dummy, aligned_dummy, mask_or_null ? aligned_dummy : nullptr,
+                      aligned_dummy, B, L, F, head_dim, chunk_hint, flags);
+    if (rc != FA_B200_OK) return rc;
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device) {
+        e = cudaSetDevice(device);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    const size_t bytes = static_cast<size_t>(B) * L * F * sizeof(__half);
+    const size_t mbytes = mask_or_null ? static_cast<size_t>(B) * L * L * sizeof(__half) : 0;
+    DeviceCtx* c = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        rc = ensure_ctx(device, &c);
+        if (rc == FA_B200_OK && c->host_stream == nullptr) {
+            e = cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+        }
+        for (int i = 0; i < 4 && rc == FA_B200_OK; ++i) rc = grow(*c, i, bytes);
+        if (rc == FA_B200_OK && mbytes) rc = grow(*c, 4, mbytes);
+    }
+    if (rc == FA_B200_OK) {
+        cudaStream_t st = c->host_stream;
+        const void* src[3] = {q, k, v};
+        for (int i = 0; i < 3 && rc == FA_B200_OK; ++i) {
+            e = cudaMemcpyAsync(c->stage[i], src[i], bytes, cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+        }
+        if (rc == FA_B200_OK && mbytes) {
+            e = cudaMemcpyAsync(c->stage[4], mask_or_null, mbytes, cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+        }
+        if (rc == FA_B200_OK)
+            rc = forward_device(c->stage[0], c->stage[1], c->stage[2], mbytes ? c->stage[4] : nullptr,
+                                c->stage[3], B, L, F, head_dim, device, st, flags & ~FA_B200_FLAG_SYNC);
+        if (rc == FA_B200_OK) {
+            e = cudaMemcpyAsync(y, c->stage[3], bytes, cudaMemcpyDeviceToHost, st);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+        }
+        e = cudaStreamSynchronize(st);
+        if (rc == FA_B200_OK && e != cudaSuccess) rc = static_cast<int>(e);
+        if (rc == FA_B200_OK) {
+            uint32_t w[2] = {0, 0};
+            e = cudaMemcpy(w, c->status, sizeof(w), cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+            else if (w[0] != 0) rc = FA_B200_ERR_DEVICE_TIMEOUT;
+        }
+    }
+    if (prev != device) (void)cudaSetDevice(prev);
+    return rc;
+}
+
+const char* fa_b200_strerror(int code) {
+    switch (code) {
+        case FA_B200_OK: return "success";
+        case FA_B200_ERR_NULL_POINTER: return "q, k, v and y must not be NULL";
+        case FA_B200_ERR_HEAD_DIM: return "head_dim must be 16, 32, 64 or 128";
+        case FA_B200_ERR_CHUNK:
+            return "chunk_size must be a power of two in [16, 128], at most 2*head_dim, and not 16 with head_dim 128";
+        case FA_B200_ERR_SHAPE: return "B, L, F must be positive, F divisible by head_dim, B and F/head_dim at most 65535";
+        case FA_B200_ERR_ALIGNMENT: return "q, k, v and y must be 16-byte aligned";
+        case FA_B200_ERR_ARCH: return "the device is not compute capability 10.x (sm_100a)";
+        case FA_B200_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
+        case FA_B200_ERR_FLAGS: return "unknown or contradictory flags";
+        case FA_B200_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired; see fa_b200_read_status";
+        case FA_B200_ERR_TOO_LARGE: return "the problem exceeds the fixed capacity of this entry point";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown fa_b200 status";
+}
+
+int fa_b200_query(int device, int32_t out[4]) {
+    if (!out) return FA_B200_ERR_NULL_POINTER;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    out[0] = prop.major;
+    out[1] = prop.minor;
+    out[2] = prop.multiProcessorCount;
+    out[3] = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+    return FA_B200_OK;
+}
+
+int fa_b200_read_status(int device, uint32_t out[2]) {
+    if (!out) return FA_B200_ERR_NULL_POINTER;
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    int rc = FA_B200_OK;
+    DeviceCtx* c = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        rc = ensure_ctx(device, &c);
+    }
+    if (rc == FA_B200_OK) {
+        e = cudaDeviceSynchronize();
+        if (e == cudaSuccess) e = cudaMemcpy(out, c->status, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemset(c->status, 0, 2 * sizeof(uint32_t));
+        if (e != cudaSuccess) rc = static_cast<int>(e);
+    }
+    if (prev != device) (void)cudaSetDevice(prev);
+    return rc;
+}
+
+int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim, int has_mask,
+                          uint32_t flags) {
+    alignas(16) static const char d[16] = {0};
+    const int rc = validate(d, d, d, has_mask ? d : nullptr, d, B, L, F, head_dim, 0, flags);
+    if (rc != FA_B200_OK) return rc;
+    return select_kernel(B, L, F, head_dim, has_mask != 0, flags, 148);
+}
+
+}  // extern "C"

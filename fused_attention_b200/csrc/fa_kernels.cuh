@@ -1,0 +1,581 @@
+// Fused multi-head attention forward for sm_100a:  Y = softmax(Q K^T / sqrt(H)) V.
+//
+// Two kernels share the same arithmetic:
+//   fa_fwd_simple<H, kHasMask>  one 128-row query tile per CTA, 128 threads, every step in program
+//                               order.  Covers every head_dim (16, 32, 64, 128), the additive mask
+//                               and tiny problems; several CTAs per SM overlap one another.
+//   fa_fwd_pipelined<H>         two 128-row query tiles per CTA, 512 threads split into roles
+//                               (2 softmax warpgroups, 1 correction warpgroup, 1 MMA warp, 1 TMA
+//                               warp); K/V stream through a shared-memory ring; the softmax of one
+//                               tile overlaps the MMAs of the other.  H in {64, 128}, no mask.
+//
+// What they replace in the reference (include/fused_attn.cuh): attention_kernel (605-858) and the
+// threadblock_* primitives it calls (48-521).  The maths is the reference's blockwise merge of
+// (row max, row sum, numerator) (458-521; README.md:45-61) with these deliberate differences:
+// fp32 scores, running max, running sum and numerator (the reference keeps all of them in fp16),
+// exp2 with log2(e)/sqrt(H) folded into one multiply-add, and key tiles that may be ragged.
+//
+// Data layout.  Q, K, V, Y: [B, L, F] fp16, head h in columns [h*H, (h+1)*H).  A TMA tensor map
+// sees each input as a 3-D tensor {F, L, B}; a tile is 128 rows x H columns fetched as H/64 boxes
+// of 128 x 64 (one box of 128 x H for H < 64) with the swizzle span equal to the box row, so a box
+// lands in shared memory as 128 rows of 128 (64, 32) bytes.  Rows beyond L are zero-filled by TMA.
+// That layout is the canonical K-major operand (Q and K for S = Q K^T) and, read with the
+// MN-major bit set, the canonical operand for V in O = P V, so V is never transposed.
+//
+// TMEM (columns of 128 lanes x 32 bit): S tile 128 columns of fp32; P (fp16, two per column)
+// overwrites the first 64 columns of its S; O tile H columns of fp32.
+#pragma once
+
+#include <cuda.h>
+#include "fa_ptx.cuh"
+
+namespace fa {
+
+struct Params {
+    __half* y;            // [B, L, F]
+    const __half* mask;   // [B, L, L] or nullptr
+    uint32_t* status;     // device status word pair, see WaitCtl
+    uint32_t B, L, F;
+    uint32_t n_kv_tiles;  // ceil(L / 128)
+    float scale_log2;     // log2(e) / sqrt(H)
+    float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
+};
+
+constexpr int kTile = 128;  // rows of a query tile and of a key/value tile
+
+// role << 8 | barrier id, written to the status word when a bounded wait expires
+enum : uint32_t {
+    kRoleSimple = 0x100u,
+    kRoleProducer = 0x200u,
+    kRoleMma = 0x300u,
+    kRoleSoftmax = 0x400u,
+    kRoleCorrection = 0x500u,
+    kRoleDrain = 0x600u
+};
+
+template <int H>
+struct TileGeom {
+    static constexpr int kBoxCols = H < 64 ? H : 64;           // columns per TMA box
+    static constexpr int kBoxes = H / kBoxCols;                // boxes per tile
+    static constexpr int kSwz = kBoxCols * 2;                  // swizzle span = row pitch, bytes
+    static constexpr int kBoxBytes = kTile * kBoxCols * 2;     // 16 KiB at H >= 64
+    static constexpr int kTileBytes = kTile * H * 2;
+};
+
+// One TMA tile (all its boxes) -> shared memory at `dst`, signalling `bar`.
+template <int H>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                          int32_t col0, int32_t row0, int32_t batch) {
+    using G = TileGeom<H>;
+    mbar_expect_tx(bar, G::kTileBytes);
+#pragma unroll
+    for (int b = 0; b < G::kBoxes; ++b)
+        tma_load_3d(dst + b * G::kBoxBytes, map, bar, col0 + b * G::kBoxCols, row0, batch);
+}
+
+// S[128 x 128] = Q[128 x H] * K[128 x H]^T, both operands K-major in shared memory.
+template <int H>
+__device__ __forceinline__ void issue_qk(uint32_t tS, uint32_t sQ, uint32_t sK) {
+    using G = TileGeom<H>;
+    constexpr uint32_t idesc = make_idesc_f16(kTile, 0);
+#pragma unroll
+    for (int ks = 0; ks < H / 16; ++ks) {
+        const uint32_t off = ((ks * 16) / G::kBoxCols) * G::kBoxBytes + ((ks * 16) % G::kBoxCols) * 2;
+        mma_ss(tS, make_smem_desc<G::kSwz>(sQ + off, 16), make_smem_desc<G::kSwz>(sK + off, 16),
+               idesc, ks > 0 ? 1u : 0u);
+    }
+}
+
+// O[128 x H] (+)= P[128 x 128] * V[128 x H]; P is fp16 in TMEM, V is MN-major in shared memory.
+template <int H>
+__device__ __forceinline__ void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, uint32_t accumulate) {
+    using G = TileGeom<H>;
+    constexpr uint32_t idesc = make_idesc_f16(H, 1);
+#pragma unroll
+    for (int ks = 0; ks < kTile / 16; ++ks) {
+        // 16 key rows per step: 8 TMEM columns of packed fp16 pairs, 16 shared-memory rows.
+        mma_ts(tO, tP + ks * 8, make_smem_desc<G::kSwz>(sV + ks * 16 * G::kSwz, G::kBoxBytes),
+               idesc, (accumulate | ks) ? 1u : 0u);
+    }
+}
+
+// Maximum of one score row.
+__device__ __forceinline__ float row_max(const float (&s)[kTile]) {
+    float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+    for (int i = 4; i < kTile; i += 4) {
+        mx0 = fmaxf(mx0, s[i]);
+        mx1 = fmaxf(mx1, s[i + 1]);
+        mx2 = fmaxf(mx2, s[i + 2]);
+        mx3 = fmaxf(mx3, s[i + 3]);
+    }
+    return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
+// Running-maximum update of the online softmax.
+//   m      running raw maximum (updated);  mx  maximum of the new score row;  c  log2(e)/sqrt(H)
+// Returns alpha, the factor by which everything accumulated before this step must be multiplied,
+// and nmc = -m_new*c, the addend of the folded exponent s*c - m_new*c.
+__device__ __forceinline__ float update_max(float& m, const float mx, const float c, float& nmc) {
+    const float m_new = fmaxf(m, mx);
+    // A row that has seen nothing but -inf so far (possible only with an additive mask) keeps
+    // p = 0 and l = 0 instead of producing inf - inf.
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = ex2_approx((m - m_use) * c);
+    nmc = -m_use * c;
+    m = m_new;
+    return alpha;
+}
+
+// P = exp2(s*c + nmc) for one score row: written as fp16 into 64 TMEM columns at tP (two values
+// per column, even key index in the low half); returns the fp32 row sum of P.
+__device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const float c,
+                                                 const float nmc, const uint32_t tP) {
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float p0 = ex2_approx(fmaf(s[chunk * 32 + 2 * e], c, nmc));
+            const float p1 = ex2_approx(fmaf(s[chunk * 32 + 2 * e + 1], c, nmc));
+            sum0 += p0;
+            sum1 += p1;
+            pk[e] = pack_half2(p0, p1);
+        }
+        tmem_st16(tP + chunk * 16, pk);
+    }
+    return sum0 + sum1;
+}
+
+// Read one O row from TMEM, multiply by `f`, write it back.
+template <int H>
+__device__ __forceinline__ void rescale_o_row(uint32_t tO, float f) {
+#pragma unroll
+    for (int c0 = 0; c0 < H; c0 += 32) {
+        float o[32];
+        if constexpr (H % 32 == 0) {
+            tmem_ld32(tO + c0, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= f;
+            tmem_st32(tO + c0, o);
+        } else {  // H == 16
+            tmem_ld16(tO + c0, o);
+            tmem_wait_ld();
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(o[i] * f);
+            tmem_st16(tO + c0, w);
+        }
+    }
+}
+
+// Read one O row from TMEM, multiply by `inv_l`, convert to fp16 and store it with 16-byte stores.
+template <int H>
+__device__ __forceinline__ void store_o_row(uint32_t tO, float inv_l, __half* dst, bool valid) {
+#pragma unroll
+    for (int c0 = 0; c0 < H; c0 += 32) {
+        float o[32];
+        constexpr int n = (H % 32 == 0) ? 32 : 16;
+        if constexpr (n == 32) {
+            tmem_ld32(tO + c0, o);
+        } else {
+            tmem_ld16(tO + c0, o);
+        }
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+            for (int i = 0; i < n; i += 8) {
+                uint4 w;
+                w.x = pack_half2(o[i] * inv_l, o[i + 1] * inv_l);
+                w.y = pack_half2(o[i + 2] * inv_l, o[i + 3] * inv_l);
+                w.z = pack_half2(o[i + 4] * inv_l, o[i + 5] * inv_l);
+                w.w = pack_half2(o[i + 6] * inv_l, o[i + 7] * inv_l);
+                *reinterpret_cast<uint4*>(dst + c0 + i) = w;
+            }
+        }
+    }
+}
+
+// Scores of one row (TMEM -> registers).
+__device__ __forceinline__ void load_s_row(uint32_t tS, float (&s)[kTile]) {
+    tmem_ld32(tS, s);
+    tmem_ld32(tS + 32, s + 32);
+    tmem_ld32(tS + 64, s + 64);
+    tmem_ld32(tS + 96, s + 96);
+    tmem_wait_ld();
+}
+
+// Columns at or beyond `valid` belong to keys past the end of the sequence.
+__device__ __forceinline__ void mask_tail(float (&s)[kTile], int valid) {
+#pragma unroll
+    for (int i = 0; i < kTile; ++i)
+        if (i >= valid) s[i] = -INFINITY;
+}
+
+// ============================================================================ simple kernel
+// grid = (ceil(L/128), R, B), block = 128.  Thread t owns query row t of the tile (TMEM lane t).
+template <int H, bool kHasMask>
+__global__ void __launch_bounds__(128)
+fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const Params p) {
+    using G = TileGeom<H>;
+    constexpr uint32_t kTmemCols = 256;  // S/P in [0,128), O in [128, 128+H)
+    enum { BAR_Q = 0, BAR_K, BAR_V, BAR_S, BAR_O, BAR_COUNT };
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[BAR_COUNT];
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_flag;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5;
+    const uint32_t q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+    const int32_t col0 = static_cast<int32_t>(head * H);
+    const int32_t q_row0 = static_cast<int32_t>(q_tile * kTile);
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = smem_base, sK = sQ + G::kTileBytes, sV = sK + G::kTileBytes;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    const WaitCtl ctl{p.status, &abort_flag};
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t lane_off = (warp * 32u) << 16;
+    const uint32_t tS = tmem_base + lane_off;          // this thread's score row
+    const uint32_t tO = tmem_base + lane_off + 128u;   // this thread's output row
+    const uint32_t n_tiles = p.n_kv_tiles;
+
+    if (tid == 0) {
+        load_tile<H>(sQ, &tmQ, bar(BAR_Q), col0, q_row0, batch);
+        load_tile<H>(sK, &tmK, bar(BAR_K), col0, 0, batch);
+        load_tile<H>(sV, &tmV, bar(BAR_V), col0, 0, batch);
+    }
+
+    float m = -INFINITY, l = 0.f;
+    const uint32_t q_row = q_tile * kTile + tid;
+    const bool row_valid = q_row < p.L;
+
+    for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t ph = j & 1u;
+        if (tid == 0) {
+            if (j == 0) mbar_wait(bar(BAR_Q), 0, ctl, kRoleSimple | BAR_Q);
+            mbar_wait(bar(BAR_K), ph, ctl, kRoleSimple | BAR_K);
+            tc_fence_after();
+            issue_qk<H>(tmem_base, sQ, sK);
+            tc_commit(bar(BAR_S));
+        }
+        mbar_wait(bar(BAR_S), ph, ctl, kRoleSimple | BAR_S);
+        tc_fence_after();
+        // The K tile is free again: fetch the next one while the softmax runs.
+        if (tid == 0 && j + 1 < n_tiles)
+            load_tile<H>(sK, &tmK, bar(BAR_K), col0, static_cast<int32_t>((j + 1) * kTile), batch);
+
+        float s[kTile];
+        __syncwarp();
+        load_s_row(tS, s);
+        if constexpr (kHasMask) {
+            // additive mask row: mask[batch, q_row, j*128 + i], shared by all heads
+            if (row_valid) {
+                const __half* mrow = p.mask + (static_cast<size_t>(batch) * p.L + q_row) * p.L +
+                                     static_cast<size_t>(j) * kTile;
+                const int valid = min(static_cast<int>(p.L - j * kTile), kTile);
+#pragma unroll
+                for (int i = 0; i < kTile; ++i)
+                    if (i < valid) s[i] = fmaf(__half2float(mrow[i]), p.mask_to_score, s[i]);
+            }
+        }
+        if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
+        float nmc;
+        const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
+        l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
+        if (j > 0) rescale_o_row<H>(tO, alpha);  // PV(j-1) finished: BAR_O was waited below
+        tmem_wait_st();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            mbar_wait(bar(BAR_V), ph, ctl, kRoleSimple | BAR_V);
+            issue_pv<H>(tmem_base + 128u, tmem_base, sV, j > 0 ? 1u : 0u);
+            tc_commit(bar(BAR_O));
+        }
+        mbar_wait(bar(BAR_O), ph, ctl, kRoleSimple | BAR_O);
+        tc_fence_after();
+        __syncwarp();
+        if (tid == 0 && j + 1 < n_tiles)
+            load_tile<H>(sV, &tmV, bar(BAR_V), col0, static_cast<int32_t>((j + 1) * kTile), batch);
+    }
+
+    // Y = O / l
+    {
+        __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
+        store_o_row<H>(tO, 1.f / l, dst, row_valid);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ============================================================================ pipelined kernel
+template <int H>
+struct PipeCfg {
+    using G = TileGeom<H>;
+    static constexpr int kStages = H == 128 ? 4 : 8;   // ring slots of one K or V tile each
+    static constexpr int kQBytes = 2 * G::kTileBytes;  // two query tiles
+    static constexpr int kRingBytes = kStages * G::kTileBytes;
+    static constexpr int kSmemBytes = kQBytes + kRingBytes + 1024;  // + alignment slack
+    static constexpr uint32_t kTmemCols = 512;
+    // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+H) O1 [384,384+H)
+    static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+};
+
+// grid = (ceil(L/256), R, B), block = 512.
+// warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1; 8-11: correction + epilogue;
+// 12: MMA issue (one thread) and TMEM owner; 13: TMA producer (one thread); 14-15: idle.
+template <int H>
+__global__ void __launch_bounds__(512, 1)
+fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const Params p) {
+    using G = TileGeom<H>;
+    using C = PipeCfg<H>;
+    constexpr int NS = C::kStages;
+    enum {
+        BAR_Q0 = 0, BAR_Q1,          // TMA -> MMA: query tile landed
+        BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
+        BAR_P0, BAR_P1,              // softmax -> MMA: P tile written (128 arrivals)
+        BAR_PV0, BAR_PV1,            // MMA -> correction: P V of this step complete
+        BAR_OK0, BAR_OK1,            // correction -> MMA: O rescaled for this step (128 arrivals)
+        BAR_A0, BAR_A1,              // softmax -> correction: alpha (or final l) in shared memory
+        BAR_FINAL,                   // MMA -> itself: every MMA retired
+        BAR_FULL,                    // NS ring barriers TMA -> MMA
+        BAR_EMPTY = BAR_FULL + NS,   // NS ring barriers MMA -> TMA
+        BAR_COUNT = BAR_EMPTY + NS
+    };
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[BAR_COUNT];
+    __shared__ float alpha_buf[2][2][kTile];  // [tile][step parity][row]
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_flag;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5;
+    const uint32_t lane = tid & 31u;
+    const uint32_t q_pair = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+    const int32_t col0 = static_cast<int32_t>(head * H);
+    const uint32_t n_tiles = p.n_kv_tiles;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = smem_base;                   // two tiles
+    const uint32_t sRing = smem_base + C::kQBytes;   // NS tiles
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    const WaitCtl ctl{p.status, &abort_flag};
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < BAR_COUNT; ++i) {
+            const bool many = (i == BAR_P0 || i == BAR_P1 || i == BAR_OK0 || i == BAR_OK1 ||
+                               i == BAR_A0 || i == BAR_A1);
+            mbar_init(bar(i), many ? 128u : 1u);
+        }
+        abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
+    if (warp == 12) {
+        tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------------ softmax, tile i
+        setmaxnreg_inc<192>();
+        const uint32_t i = warp >> 2;
+        const uint32_t row = tid & 127u;
+        const uint32_t tS = tmem_base + (((warp & 3u) * 32u) << 16) + (i ? C::kColS1 : C::kColS0);
+        float m = -INFINITY, l = 0.f;
+        for (uint32_t j = 0; j < n_tiles; ++j) {
+            mbar_wait(bar(BAR_S0 + i), j & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
+            tc_fence_after();
+            __syncwarp();
+            float s[kTile];
+            load_s_row(tS, s);
+            if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
+            // alpha is needed by the correction warps before P is needed by the MMA: publish it
+            // first.  It only depends on the row maximum.
+            float nmc;
+            const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
+            if (j > 0) {
+                alpha_buf[i][j & 1u][row] = alpha;
+                mbar_arrive(bar(BAR_A0 + i));
+            }
+            l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_P0 + i));
+        }
+        alpha_buf[i][n_tiles & 1u][row] = l;
+        mbar_arrive(bar(BAR_A0 + i));
+    } else if (warp < 12) {
+        // ------------------------------------------------------------------ correction + epilogue
+        setmaxnreg_dec<64>();
+        const uint32_t row = tid & 127u;
+        const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
+        for (uint32_t j = 1; j < n_tiles; ++j) {
+#pragma unroll
+            for (uint32_t i = 0; i < 2; ++i) {
+                const uint32_t ph = (j - 1) & 1u;
+                mbar_wait(bar(BAR_A0 + i), ph, ctl, kRoleCorrection | (BAR_A0 + i));
+                const float alpha = alpha_buf[i][j & 1u][row];
+                mbar_wait(bar(BAR_PV0 + i), ph, ctl, kRoleCorrection | (BAR_PV0 + i));
+                tc_fence_after();
+                __syncwarp();
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                    rescale_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), alpha);
+                    tmem_wait_st();
+                }
+                tc_fence_before();
+                mbar_arrive(bar(BAR_OK0 + i));
+            }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 2; ++i) {
+            const uint32_t ph = (n_tiles - 1) & 1u;
+            mbar_wait(bar(BAR_A0 + i), ph, ctl, kRoleCorrection | (BAR_A0 + i));
+            const float l = alpha_buf[i][n_tiles & 1u][row];
+            mbar_wait(bar(BAR_PV0 + i), ph, ctl, kRoleCorrection | (BAR_PV0 + i));
+            tc_fence_after();
+            __syncwarp();
+            const uint32_t q_row = (q_pair * 2u + i) * kTile + row;
+            __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
+            store_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), 1.f / l, dst,
+                           q_row < p.L);
+        }
+    } else {
+        setmaxnreg_dec<64>();
+        if (warp == 12 && lane == 0) {
+            // -------------------------------------------------------------- MMA issue
+            const uint32_t tS0 = tmem_base + C::kColS0, tS1 = tmem_base + C::kColS1;
+            const uint32_t tO0 = tmem_base + C::kColO0, tO1 = tmem_base + C::kColO1;
+            auto slot_addr = [&](uint32_t t) { return sRing + (t % NS) * G::kTileBytes; };
+            auto wait_full = [&](uint32_t t) {
+                mbar_wait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
+            };
+            auto free_slot = [&](uint32_t t) { tc_commit(bar(BAR_EMPTY + (t % NS))); };
+            // ring item 2j is K tile j, item 2j+1 is V tile j
+            mbar_wait(bar(BAR_Q0), 0, ctl, kRoleMma | BAR_Q0);
+            wait_full(0);
+            tc_fence_after();
+            issue_qk<H>(tS0, sQ, slot_addr(0));
+            tc_commit(bar(BAR_S0));
+            mbar_wait(bar(BAR_Q1), 0, ctl, kRoleMma | BAR_Q1);
+            tc_fence_after();
+            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
+            tc_commit(bar(BAR_S1));
+            free_slot(0);
+            for (uint32_t j = 0; j < n_tiles; ++j) {
+                const uint32_t tv = 2 * j + 1, tk = 2 * j + 2;
+                const bool more = j + 1 < n_tiles;
+                const uint32_t acc = j > 0 ? 1u : 0u;
+                wait_full(tv);
+                // tile 0
+                mbar_wait(bar(BAR_P0), j & 1u, ctl, kRoleMma | BAR_P0);
+                if (j > 0) mbar_wait(bar(BAR_OK0), (j - 1) & 1u, ctl, kRoleMma | BAR_OK0);
+                tc_fence_after();
+                issue_pv<H>(tO0, tS0, slot_addr(tv), acc);
+                tc_commit(bar(BAR_PV0));
+                if (more) {
+                    wait_full(tk);
+                    tc_fence_after();
+                    issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
+                    tc_commit(bar(BAR_S0));
+                }
+                // tile 1
+                mbar_wait(bar(BAR_P1), j & 1u, ctl, kRoleMma | BAR_P1);
+                if (j > 0) mbar_wait(bar(BAR_OK1), (j - 1) & 1u, ctl, kRoleMma | BAR_OK1);
+                tc_fence_after();
+                issue_pv<H>(tO1, tS1, slot_addr(tv), acc);
+                tc_commit(bar(BAR_PV1));
+                free_slot(tv);
+                if (more) {
+                    issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                    tc_commit(bar(BAR_S1));
+                    free_slot(tk);
+                }
+            }
+            tc_commit(bar(BAR_FINAL));
+            mbar_wait(bar(BAR_FINAL), 0, ctl, kRoleMma | BAR_FINAL);
+        } else if (warp == 13 && lane == 0) {
+            // -------------------------------------------------------------- TMA producer
+            const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
+            load_tile<H>(sQ, &tmQ, bar(BAR_Q0), col0, q_row0, batch);
+            uint32_t issued = 0;
+            bool q1_issued = false;
+            const uint32_t total = 2 * n_tiles;
+            for (uint32_t t = 0; t < total; ++t) {
+                if (t == 1) {
+                    load_tile<H>(sQ + G::kTileBytes, &tmQ, bar(BAR_Q1), col0, q_row0 + kTile, batch);
+                    q1_issued = true;
+                }
+                const uint32_t slot = t % NS;
+                const bool ok = mbar_wait(bar(BAR_EMPTY + slot), ((t / NS) & 1u) ^ 1u, ctl,
+                                          kRoleProducer | (BAR_EMPTY + slot));
+                if (!ok) break;  // a wait expired somewhere: issue nothing more
+                load_tile<H>(sRing + slot * G::kTileBytes, (t & 1u) ? &tmV : &tmK, bar(BAR_FULL + slot),
+                             col0, static_cast<int32_t>((t >> 1) * kTile), batch);
+                issued = t + 1;
+            }
+            if (abort_flag != 0u) {
+                // Do not leave the CTA while one of its own copies may still be landing.
+                const uint32_t first = issued > NS ? issued - NS : 0u;
+                for (uint32_t t = first; t < issued; ++t) {
+                    const uint32_t slot = t % NS;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar(BAR_FULL + slot), (t / NS) & 1u) &&
+                           clock64() - t0 < 200000000LL) {
+                    }
+                }
+                const long long t0 = clock64();
+                while (!(mbar_try_wait(bar(BAR_Q0), 0) && (!q1_issued || mbar_try_wait(bar(BAR_Q1), 0))) &&
+                       clock64() - t0 < 200000000LL) {
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+}  // namespace fa

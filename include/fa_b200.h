@@ -1,0 +1,117 @@
+/*
+ * fa_b200.h — C ABI of the B200 (sm_100a) fused multi-head attention forward.
+ *
+ * One operator:  Y = softmax(Q K^T / sqrt(H)) V  per (batch, head), fp16 in / fp16 out,
+ * fp32 accumulation and fp32 online-softmax state, no L x L score matrix in global memory.
+ *
+ * Tensor contract (same as the reference operator, src/fused_attn_extention.cu:24-70):
+ * q, k, v, y are contiguous fp16 device arrays of logical shape [B, L, F] with F = R * head_dim;
+ * head h owns columns [h*head_dim, (h+1)*head_dim) of the last axis
+ * (include/fused_attn.cuh:681-696 in the reference).  The optional mask is a contiguous fp16
+ * array [B, L, L] that is ADDED to the scaled scores of every head (reference
+ * include/fused_attn.cuh:686,735-742; the reference adds it to the first key chunk only, this
+ * library adds it to every key tile).
+ *
+ * Every function is thread-safe.  None of them terminates the process: where the reference
+ * launcher prints and calls exit() (include/fused_attn.cuh:17-42) these return a status code.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  0 = success, negative = rejected before launch, positive = a cudaError_t. */
+enum {
+    FA_B200_OK = 0,
+    FA_B200_ERR_NULL_POINTER = -1,   /* q, k, v or y is NULL                                   */
+    FA_B200_ERR_HEAD_DIM = -2,       /* head_dim not in {16, 32, 64, 128}                      */
+    FA_B200_ERR_CHUNK = -3,          /* chunk_hint violates the reference's rule set           */
+    FA_B200_ERR_SHAPE = -4,          /* B, L or F is zero, F % head_dim != 0, or too large     */
+    FA_B200_ERR_ALIGNMENT = -5,      /* a tensor base address is not 16-byte aligned           */
+    FA_B200_ERR_ARCH = -6,           /* the device is not compute capability 10.x              */
+    FA_B200_ERR_DRIVER = -7,         /* cuTensorMapEncodeTiled unavailable or failed           */
+    FA_B200_ERR_FLAGS = -8,          /* contradictory or unknown flag bits                     */
+    FA_B200_ERR_DEVICE_TIMEOUT = -9, /* a bounded device-side wait expired (see read_status)   */
+    FA_B200_ERR_TOO_LARGE = -10      /* a fixed-capacity entry point was given too much work   */
+};
+
+/* flags for fa_b200_attention_forward */
+enum {
+    FA_B200_FLAG_DEFAULT = 0u,
+    FA_B200_FLAG_FORCE_SIMPLE = 1u,    /* always use the one-tile-per-CTA kernel                */
+    FA_B200_FLAG_FORCE_PIPELINED = 2u, /* always use the warp-specialised kernel (H in {64,128}) */
+    FA_B200_FLAG_SYNC = 4u             /* synchronise the stream before returning and fold the
+                                          device status word into the return value             */
+};
+
+/*
+ * Launch the fused attention forward on `cuda_stream` (a cudaStream_t, NULL = default stream)
+ * of CUDA device `device`.  Asynchronous unless FA_B200_FLAG_SYNC is given.
+ *
+ * Replaces the reference's launcher template
+ *   launch_attention_kernel<head_dim, chunk_size>(B, L, F, q, k, v, mask, out, sync)
+ * (include/fused_attn.cuh:860-894) together with the 12-way dispatch switch of
+ * src/fused_attn_extention.cu:72-111.
+ *
+ * `chunk_hint` is validated with the reference's rules (power of two in [16,128], <= 2*head_dim,
+ * not (16 with head_dim 128); src/fused_attn_extention.cu:45-47) so that existing callers see
+ * the same rejections, but the tile sizes are internal and L need NOT be a multiple of it.
+ * Pass 0 to skip the check.
+ */
+int fa_b200_attention_forward(const void* q, const void* k, const void* v,
+                              const void* mask_or_null, void* y,
+                              uint32_t B, uint32_t L, uint32_t F,
+                              uint32_t head_dim, uint32_t chunk_hint,
+                              int device, void* cuda_stream, uint32_t flags);
+
+/*
+ * Same operator with HOST buffers: copies q, k, v (and mask) to the device, runs the kernel and
+ * copies y back, all on one internal stream, and returns when y is complete.  The device
+ * staging buffers are cached per device and grow on demand.  This is the call a torch-free
+ * host program makes; it plays the role of the reference's standalone driver
+ * (src/test.cu:43-62: cudaMalloc, fill, launch, synchronise).
+ */
+int fa_b200_attention_forward_host(const void* q, const void* k, const void* v,
+                                   const void* mask_or_null, void* y,
+                                   uint32_t B, uint32_t L, uint32_t F,
+                                   uint32_t head_dim, uint32_t chunk_hint,
+                                   int device, uint32_t flags);
+
+/*
+ * Human-readable text for a status code returned by this library (negative codes) or by the
+ * CUDA runtime (positive codes).  Replaces the stderr printing of the reference's
+ * checkCudaError / checkLastCudaError (include/fused_attn.cuh:17-42).
+ */
+const char* fa_b200_strerror(int code);
+
+/*
+ * Device facts used by harnesses: out[0] = compute capability major, out[1] = minor,
+ * out[2] = SM count, out[3] = max opt-in shared memory per block (bytes).
+ * No counterpart in the reference (its CMake probes the device instead, CMakeLists.txt:12-39).
+ */
+int fa_b200_query(int device, int32_t out[4]);
+
+/*
+ * Read and clear the per-device status word written by kernels whose bounded waits expired:
+ * out[0] = first failure code (0 = none; bits 8.. = role, bits 0..7 = barrier id),
+ * out[1] = number of CTAs that reported.  Synchronises the device.
+ * No counterpart in the reference (it has no device-side error reporting).
+ */
+int fa_b200_read_status(int device, uint32_t out[2]);
+
+/*
+ * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
+ * kernel, 2 for the warp-specialised kernel, negative status on invalid arguments.
+ * No counterpart in the reference.
+ */
+int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
+                          int has_mask, uint32_t flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
