@@ -20,6 +20,7 @@ EXPORTED_SYMBOLS = (
     "fa_b200_query",
     "fa_b200_read_status",
     "fa_b200_select_kernel",
+    "fa_b200_selftest_bounded_wait",
 )
 
 # Status codes and flags, mirrored from include/fa_b200.h.
@@ -71,6 +72,8 @@ def load() -> ctypes.CDLL:
         lib.fa_b200_query.argtypes = [i32, ctypes.POINTER(ctypes.c_int32)]
         lib.fa_b200_read_status.restype = i32
         lib.fa_b200_read_status.argtypes = [i32, ctypes.POINTER(ctypes.c_uint32)]
+        lib.fa_b200_selftest_bounded_wait.restype = i32
+        lib.fa_b200_selftest_bounded_wait.argtypes = [i32, ctypes.POINTER(ctypes.c_uint32)]
         lib.fa_b200_select_kernel.restype = i32
         lib.fa_b200_select_kernel.argtypes = [u32, u32, u32, u32, i32, u32]
         _lib = lib

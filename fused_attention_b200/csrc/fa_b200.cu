@@ -367,6 +367,29 @@ int fa_b200_read_status(int device, uint32_t out[2]) {
     return rc;
 }
 
+int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]) {
+    if (!out) return FA_B200_ERR_NULL_POINTER;
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    int rc = FA_B200_OK;
+    uint32_t* scratch = nullptr;  // {status code, reporting CTAs, returned marker}
+    e = cudaMalloc(reinterpret_cast<void**>(&scratch), 3 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(scratch, 0, 3 * sizeof(uint32_t));
+    if (e == cudaSuccess) {
+        // 20 million cycles: about 10 ms
+        fa::fa_selftest_bounded_wait<<<1, 32>>>(scratch, fa::kRoleDrain | 0x7Fu, 20000000LL, scratch + 2);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(out, scratch, 3 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (scratch) (void)cudaFree(scratch);
+    if (e != cudaSuccess) rc = static_cast<int>(e);
+    if (prev != device) (void)cudaSetDevice(prev);
+    return rc;
+}
+
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim, int has_mask,
                           uint32_t flags) {
     alignas(16) static const char d[16] = {0};

@@ -239,7 +239,7 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t sQ = smem_base, sK = sQ + G::kTileBytes, sV = sK + G::kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    const WaitCtl ctl{p.status, &abort_flag};
+    const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles};
 
     if (tid == 0) {
 #pragma unroll
@@ -390,7 +390,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t sRing = smem_base + C::kQBytes;   // NS tiles
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    const WaitCtl ctl{p.status, &abort_flag};
+    const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles};
 
     if (tid == 0) {
 #pragma unroll
@@ -576,6 +576,24 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
+}
+
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing ever completes, with a
+// short cap.  The wait must give up, record `code` in the status word and return normally.
+__global__ void fa_selftest_bounded_wait(uint32_t* status, uint32_t code, long long cap_cycles,
+                                         uint32_t* returned) {
+    __shared__ __align__(8) uint64_t bar_mem;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar_mem), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const WaitCtl ctl{status, &abort_flag, cap_cycles};
+    const bool ok = mbar_wait(smem_u32(&bar_mem), 0, ctl, code);
+    __syncthreads();
+    if (threadIdx.x == 0) *returned = ok ? 1u : 2u;  // 2 = gave up, as it must
 }
 
 }  // namespace fa

@@ -45,6 +45,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 struct WaitCtl {
     uint32_t* status;              // global: [0] first failure code, [1] number of reporting CTAs
     volatile uint32_t* abort_flag; // shared: non-zero once any wait of this CTA has expired
+    long long cap_cycles;          // how long one wait may spin
 };
 
 // About two seconds at 2 GHz; a whole launch of the largest supported problem takes milliseconds.
@@ -57,7 +58,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Wa
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0u) {
             if (*ctl.abort_flag != 0u) return false;
-            if (clock64() - t0 > kWaitCapCycles) {
+            if (clock64() - t0 > ctl.cap_cycles) {
                 if (atomicExch(const_cast<uint32_t*>(ctl.abort_flag), 1u) == 0u) {
                     atomicCAS(ctl.status, 0u, code);
                     atomicAdd(ctl.status + 1, 1u);

@@ -104,6 +104,15 @@ int fa_b200_query(int device, int32_t out[4]);
 int fa_b200_read_status(int device, uint32_t out[2]);
 
 /*
+ * Exercise the bounded-wait path without touching the attention kernels: a one-warp kernel waits
+ * (for about 10 ms) on a barrier that nothing completes, must give up, report and return.
+ * out[0] = status code it recorded (expected 0x67F), out[1] = CTAs that reported (expected 1),
+ * out[2] = 2 if the wait returned "gave up", 1 if it claimed success.  The GPU stays usable.
+ * No counterpart in the reference (its kernels wait only on __syncthreads).
+ */
+int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]);
+
+/*
  * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
  * kernel, 2 for the warp-specialised kernel, negative status on invalid arguments.
  * No counterpart in the reference.

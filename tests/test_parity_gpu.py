@@ -1,0 +1,263 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the reference's golden outputs.
+
+Tolerance (fp16 operator against the fp32 oracle on the same fp16-rounded inputs):
+max-abs <= 2e-3 and mean-abs <= 2e-4.
+"""
+import ctypes
+import glob
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import fused_attention_b200 as fa
+from fused_attention_b200 import _lib
+from fused_attention_b200.workloads import WORKLOADS, make_inputs, workload_inputs
+from oracle.naive_attention import MAX_ABS_TOL, MEAN_ABS_TOL, attention as oracle, error_metrics
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+SIMPLE, PIPE = _lib.FLAG_FORCE_SIMPLE, _lib.FLAG_FORCE_PIPELINED
+
+
+def run(q, k, v, H, mask=None, flags=0, chunk=None):
+    chunk = chunk or (32 if H == 128 else 16)
+    out = fa.attention_forward(H, chunk, q.cuda(), k.cuda(), v.cuda(),
+                               None if mask is None else mask.cuda(), flags=flags | _lib.FLAG_SYNC)
+    return out.float().cpu()
+
+
+def assert_close(y, expected):
+    assert not torch.isnan(y).any()
+    m = error_metrics(y, expected)
+    assert m["max_abs"] <= MAX_ABS_TOL, m
+    assert m["mean_abs"] <= MEAN_ABS_TOL, m
+    return m
+
+
+@pytest.fixture(autouse=True)
+def status_word_stays_clear():
+    yield
+    assert fa.read_status(0) == (0, 0)
+
+
+def kernels_for(H, L=1024):
+    return [0, SIMPLE] + ([PIPE] if H >= 64 else [])
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_golden_vectors_of_the_reference(path):
+    d = np.load(path)
+    q, k, v = (torch.from_numpy(d[n]) for n in "qkv")
+    H = int(d["head_dim"])
+    for flags in kernels_for(H):
+        assert_close(run(q, k, v, H, flags=flags), torch.from_numpy(d["y"]))
+
+
+@pytest.mark.parametrize("name", ["tiny", "bert_base", "vit_l16_ragged"])
+def test_benchmark_configurations_full_oracle(name):
+    w = WORKLOADS[name]
+    q, k, v = workload_inputs(w)
+    expected = oracle(q, k, v, w.H)
+    for flags in kernels_for(w.H):
+        assert_close(run(q, k, v, w.H, flags=flags), expected)
+
+
+@pytest.mark.parametrize("name", ["llama7b_prefill", "long_context"])
+def test_full_size_configurations_sampled_rows(name):
+    """Every head and batch, 96 seeded query rows (plus first and last) against all keys."""
+    w = WORKLOADS[name]
+    q, k, v = workload_inputs(w)
+    g = torch.Generator().manual_seed(w.seed)
+    rows = sorted(set(torch.randint(0, w.L, (96,), generator=g).tolist()) | {0, 127, 128, w.L - 1})
+    expected = oracle(q, k, v, w.H, query_rows=rows)
+    rms = float(expected.double().pow(2).mean().sqrt())
+    for flags in (0, SIMPLE):
+        y = run(q, k, v, w.H, flags=flags)[:, rows]
+        m = assert_close(y, expected)
+        # outputs are small at these shapes: also bound the error relative to rms(Y)
+        assert m["max_abs"] / rms < 2e-2, m
+
+
+@pytest.mark.parametrize("H", [16, 32, 64, 128])
+@pytest.mark.parametrize("L", [1, 2, 31, 127, 128, 129, 255, 256, 257, 383, 385, 640])
+def test_ragged_lengths(H, L):
+    q, k, v = make_inputs(2, L, 3 * H, 1.0, 1000 + L)
+    expected = oracle(q, k, v, H)
+    for flags in kernels_for(H):
+        assert_close(run(q, k, v, H, flags=flags), expected)
+
+
+def test_many_batches_and_heads_index_correctly():
+    # every (batch, head) pair gets its own inputs; a wrong offset shows as a large error
+    q, k, v = make_inputs(5, 200, 7 * 64, 1.0, 77)
+    expected = oracle(q, k, v, 64)
+    for flags in (SIMPLE, PIPE):
+        assert_close(run(q, k, v, 64, flags=flags), expected)
+
+
+def test_large_logits_stay_finite():
+    # sigma 4 at H=128 gives scores of a few hundred before scaling: exercises the running max
+    q, k, v = make_inputs(1, 512, 256, 4.0, 5)
+    expected = oracle(q, k, v, 128)
+    for flags in (SIMPLE, PIPE):
+        y = run(q, k, v, 128, flags=flags)
+        assert torch.isfinite(y).all()
+        m = error_metrics(y, expected)
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m   # |V| reaches 16 here
+
+
+def test_kernels_agree_and_are_deterministic():
+    q, k, v = make_inputs(2, 700, 256, 1.0, 11)
+    a = run(q, k, v, 128, flags=PIPE)
+    b = run(q, k, v, 128, flags=PIPE)
+    c = run(q, k, v, 128, flags=SIMPLE)
+    assert torch.equal(a, b)
+    assert float((a - c).abs().max()) <= 1e-3
+
+
+@pytest.mark.parametrize("H", [16, 64, 128])
+@pytest.mark.parametrize("L", [64, 200, 300])
+def test_additive_mask(H, L):
+    """Mask applied to every key tile; parity with the reference is unpinned for masks (its naive
+    function takes none), so the oracle's formula scores + mask is the definition."""
+    q, k, v = make_inputs(2, L, 2 * H, 1.0, 300 + L)
+    mask = torch.zeros(2, L, L, dtype=torch.float16)
+    mask[0] = torch.triu(torch.full((L, L), float("-inf")), diagonal=1).half()   # causal
+    mask[1, :, L - L // 3:] = float("-inf")                                        # padding
+    mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(1)).half()
+    expected = oracle(q, k, v, H, mask)
+    assert_close(run(q, k, v, H, mask=mask), expected)
+
+
+def test_value_of_ones_gives_ones_at_full_size():
+    w = WORKLOADS["llama7b_prefill"]
+    q, k, _ = workload_inputs(w)
+    v = torch.ones_like(q)
+    y = run(q, k, v, w.H)
+    assert float((y - 1.0).abs().max()) <= 1e-3
+
+
+def test_linearity_in_values_at_full_size():
+    w = WORKLOADS["llama7b_prefill"]
+    q, k, v1 = workload_inputs(w)
+    v2 = make_inputs(w.B, w.L, w.F, w.sigma, 999)[0]
+    dq, dk = q.cuda(), k.cuda()
+    f = lambda v: fa.attention_forward(w.H, 128, dq, dk, v.cuda()).float()
+    lhs = f((v1.float() * 0.5 + v2.float() * 0.25).half())
+    rhs = 0.5 * f(v1) + 0.25 * f(v2)
+    torch.cuda.synchronize()
+    assert float((lhs - rhs).abs().max()) <= 1e-3
+
+
+def test_key_permutation_invariance_at_full_size():
+    w = WORKLOADS["long_context"]
+    q, k, v = workload_inputs(w, heads=slice(0, 8))
+    perm = torch.randperm(w.L, generator=torch.Generator().manual_seed(3))
+    a = run(q, k, v, w.H)
+    b = run(q, k[:, perm].contiguous(), v[:, perm].contiguous(), w.H)
+    assert float((a - b).abs().max()) <= 5e-4
+
+
+def test_host_buffer_entry_point_matches_device_entry_point():
+    q, k, v = make_inputs(2, 300, 256, 1.0, 21)
+    y_dev = run(q, k, v, 128)
+    y_host = fa.attention_forward_host(128, 128, q.pin_memory(), k.pin_memory(), v.pin_memory()).float()
+    assert torch.equal(y_dev, y_host)
+    mask = torch.zeros(2, 300, 300, dtype=torch.float16)
+    mask[:, :, 250:] = float("-inf")
+    y_host_m = fa.attention_forward_host(128, 128, q, k, v, mask).float()
+    assert torch.equal(run(q, k, v, 128, mask=mask), y_host_m)
+
+
+def test_non_default_stream_and_output_placement():
+    q, k, v = (t.cuda() for t in make_inputs(1, 512, 256, 1.0, 31))
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        y = fa.attention_forward(128, 64, q, k, v)
+    s.synchronize()
+    assert y.device == q.device and y.dtype == torch.float16 and y.shape == q.shape
+    assert torch.equal(y, fa.attention_forward(128, 64, q, k, v))
+
+
+def test_error_behaviour_on_gpu_tensors():
+    q, k, v = (t.cuda() for t in make_inputs(1, 64, 128, 1.0, 41))
+    with pytest.raises(RuntimeError):
+        fa.attention_forward(48, 32, q, k, v)                 # head_dim not a power of two
+    with pytest.raises(RuntimeError):
+        fa.attention_forward(128, 16, q, k, v)                # forbidden pair
+    with pytest.raises(RuntimeError):
+        fa.attention_forward(64, 64, q, k[:, :32].contiguous(), v)
+    with pytest.raises(RuntimeError):
+        fa.attention_forward(64, 64, q.float(), k.float(), v.float())
+    with pytest.raises(RuntimeError):
+        fa.attention_forward(64, 64, q.transpose(1, 2), k, v)  # not contiguous
+
+
+def test_bounded_wait_gives_up_and_reports_without_harming_the_gpu():
+    out = (ctypes.c_uint32 * 3)()
+    assert _lib.load().fa_b200_selftest_bounded_wait(0, out) == 0
+    assert (out[0], out[1], out[2]) == (0x67F, 1, 2)
+    # the context is still usable
+    q, k, v = make_inputs(1, 128, 64, 1.0, 51)
+    assert_close(run(q, k, v, 64), oracle(q, k, v, 64))
+
+
+# ---------------------------------------------------------------- drop-in module `fused_attn`
+def _fused_attn_module():
+    ext_dir = os.path.join(os.path.dirname(fa.__file__), "ext")
+    if ext_dir not in sys.path:
+        sys.path.insert(0, ext_dir)
+    import fused_attn
+    return fused_attn
+
+
+@pytest.mark.parametrize("H,C", [(16, 16), (16, 32), (32, 16), (32, 32), (32, 64), (64, 16), (64, 32), (64, 64),
+                                 (64, 128), (128, 32), (128, 64), (128, 128)])
+def test_reference_unit_tests_through_the_torch_extension(H, C):
+    """The reference's own twelve cases (tests/test_fused_attn.py:12-67): B=1, R=2, L=2*C, N(0,1)
+    inputs drawn on the GPU with seed 179, compared at its tolerance rtol=atol=1e-2."""
+    fused_attn = _fused_attn_module()
+    torch.random.manual_seed(179)
+    q, k, v = (torch.randn(1, 2 * C, 2 * H, device="cuda", dtype=torch.float16) for _ in range(3))
+    expected = oracle(q.cpu(), k.cpu(), v.cpu(), H)
+    actual = fused_attn.attention_forward(H, C, q, k, v)
+    assert actual.dtype == torch.float16 and actual.device == q.device
+    torch.testing.assert_close(actual.float().cpu(), expected, rtol=0.01, atol=0.01)
+    assert_close(actual.float().cpu(), expected)
+
+
+def test_torch_extension_accepts_mask_keyword_and_ragged_length():
+    fused_attn = _fused_attn_module()
+    q, k, v = (t.cuda() for t in make_inputs(2, 197, 128, 1.0, 61))
+    mask = torch.zeros(2, 197, 197, dtype=torch.float16, device="cuda")
+    mask[:, :, 150:] = float("-inf")
+    y = fused_attn.attention_forward(head_dim=64, chunk_size=64, queries=q, keys=k, values=v, mask=mask)
+    assert_close(y.float().cpu(), oracle(q.cpu(), k.cpu(), v.cpu(), 64, mask.cpu()))
+
+
+# ---------------------------------------------------------------- the reference's own CUDA kernel
+def _ref_wmma():
+    path = os.path.join(os.path.dirname(os.path.dirname(__file__)), "oracle", "_ref", "libref_fused_attn.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref not built (needs the reference checkout at build time)")
+    lib = ctypes.CDLL(path)
+    lib.ref_wmma_attention_forward.restype = ctypes.c_int
+    lib.ref_wmma_attention_forward.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_uint32] * 5
+    return lib
+
+
+@pytest.mark.parametrize("H,C,B,R,L", [(64, 64, 1, 4, 256), (128, 128, 2, 4, 512), (32, 32, 1, 2, 128), (64, 128, 8, 12, 512)])
+def test_against_the_reference_fused_kernel(H, C, B, R, L):
+    """Same inputs through the reference's WMMA kernel (compiled for sm_100a) at its own tolerance."""
+    lib = _ref_wmma()
+    q, k, v = (t.cuda() for t in make_inputs(B, L, R * H, 1.0, 71))
+    y_ref = torch.empty_like(q)
+    assert lib.ref_wmma_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, y_ref.data_ptr(),
+                                          B, L, R * H, H, C) == 0
+    torch.cuda.synchronize()
+    y = fa.attention_forward(H, C, q, k, v)
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
