@@ -248,16 +248,16 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
 
     # end to end: host buffers in, host buffer out, through the host entry point of the C ABI
     hy = torch.empty_like(hq).pin_memory()
-    e2e_steps = max(1, min(args.steps, 10))
-    for _ in range(2):
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 10))
+    for _ in range(2 if e2e_steps else 0):
         fa.attention_forward_host(w.H, chunk, hq, hk, hv, device=local_rank, out=hy)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         fa.attention_forward_host(w.H, chunk, hq, hk, hv, device=local_rank, out=hy)
-    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / max(1, e2e_steps))
     barrier()
-    e2e_value = total_flops / e2e_s / 1e12
+    e2e_value = total_flops / e2e_s / 1e12 if e2e_steps else None
     h2d = sum_over_ranks(3 * hq.numel() * 2)
     d2h = sum_over_ranks(hq.numel() * 2)
     status2 = fa.read_status(local_rank)
@@ -317,6 +317,7 @@ def main() -> int:
     ap.add_argument("--workload", default=None)
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement (profiling runs)")
     args = ap.parse_args()
 
     from fused_attention_b200.workloads import HEADLINE, WORKLOADS
