@@ -43,6 +43,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
+#ifdef FA_TRACE
+unsigned long long* g_trace_buf = nullptr;  // device buffer of 8 * 512 records, set by the trace hook
+uint32_t g_trace_cta = 0;
+#endif
+
 // Caller holds g_mu and has made `device` current.
 int ensure_ctx(int device, DeviceCtx** out) {
     if (device < 0 || device >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
@@ -192,6 +197,10 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
                 p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
                 p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+#ifdef FA_TRACE
+                p.trace = g_trace_buf;
+                p.trace_cta = g_trace_cta;
+#endif
                 const int which = select_kernel(B, L, F, H, mask != nullptr, flags, c->sm_count);
                 if (which == 2) {
                     rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, p, st)
@@ -389,6 +398,15 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]) {
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
 }
+
+#ifdef FA_TRACE
+// Trace builds only: choose the recording CTA and the device buffer (8 * 512 * 8 bytes).
+int fa_b200_trace_setup(void* device_buffer, uint32_t cta) {
+    g_trace_buf = static_cast<unsigned long long*>(device_buffer);
+    g_trace_cta = cta;
+    return FA_B200_OK;
+}
+#endif
 
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim, int has_mask,
                           uint32_t flags) {

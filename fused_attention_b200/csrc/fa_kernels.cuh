@@ -39,7 +39,30 @@ struct Params {
     uint32_t n_kv_tiles;  // ceil(L / 128)
     float scale_log2;     // log2(e) / sqrt(H)
     float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
+#ifdef FA_TRACE
+    unsigned long long* trace;  // [8 slots][512] (clock64 << 8 | tag) of one CTA, see FA_TRACE_EV
+    uint32_t trace_cta;         // linear block index that records
+#endif
 };
+
+// Compile with -DFA_TRACE to make one CTA of the pipelined kernel record a time line: every role
+// (slot) appends clock64() with a tag at its hand-over points.  Off in normal builds.
+#ifdef FA_TRACE
+#define FA_TRACE_DECL                                                                              \
+    uint32_t tr_n = 0;                                                                             \
+    const bool tr_on = p.trace != nullptr &&                                                       \
+        (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == p.trace_cta;
+#define FA_TRACE_EV(slot, tag)                                                                     \
+    do {                                                                                           \
+        if (tr_on && tr_n < 512) {                                                                 \
+            p.trace[(slot) * 512 + tr_n] = (static_cast<unsigned long long>(clock64()) << 8) | (tag); \
+            ++tr_n;                                                                                \
+        }                                                                                          \
+    } while (0)
+#else
+#define FA_TRACE_DECL
+#define FA_TRACE_EV(slot, tag) do {} while (0)
+#endif
 
 constexpr int kTile = 128;  // rows of a query tile and of a key/value tile
 
@@ -78,11 +101,12 @@ template <int H>
 __device__ __forceinline__ void issue_qk(uint32_t tS, uint32_t sQ, uint32_t sK) {
     using G = TileGeom<H>;
     constexpr uint32_t idesc = make_idesc_f16(kTile, 0);
+    const uint64_t dq = make_smem_desc<G::kSwz>(sQ, 16), dk = make_smem_desc<G::kSwz>(sK, 16);
 #pragma unroll
     for (int ks = 0; ks < H / 16; ++ks) {
+        // the address field counts 16-byte units, so stepping along K is an add on the low word
         const uint32_t off = ((ks * 16) / G::kBoxCols) * G::kBoxBytes + ((ks * 16) % G::kBoxCols) * 2;
-        mma_ss(tS, make_smem_desc<G::kSwz>(sQ + off, 16), make_smem_desc<G::kSwz>(sK + off, 16),
-               idesc, ks > 0 ? 1u : 0u);
+        mma_ss(tS, dq + (off >> 4), dk + (off >> 4), idesc, ks > 0 ? 1u : 0u);
     }
 }
 
@@ -91,39 +115,50 @@ template <int H>
 __device__ __forceinline__ void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, uint32_t accumulate) {
     using G = TileGeom<H>;
     constexpr uint32_t idesc = make_idesc_f16(H, 1);
+    const uint64_t dv = make_smem_desc<G::kSwz>(sV, G::kBoxBytes);
 #pragma unroll
     for (int ks = 0; ks < kTile / 16; ++ks) {
         // 16 key rows per step: 8 TMEM columns of packed fp16 pairs, 16 shared-memory rows.
-        mma_ts(tO, tP + ks * 8, make_smem_desc<G::kSwz>(sV + ks * 16 * G::kSwz, G::kBoxBytes),
-               idesc, (accumulate | ks) ? 1u : 0u);
+        mma_ts(tO, tP + ks * 8, dv + ((ks * 16 * G::kSwz) >> 4), idesc, (accumulate | ks) ? 1u : 0u);
     }
 }
 
-// Maximum of one score row.
+// Maximum of one score row (3-input max: two elements per instruction, four chains).
 __device__ __forceinline__ float row_max(const float (&s)[kTile]) {
-    float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+    float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+    float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-    for (int i = 4; i < kTile; i += 4) {
-        mx0 = fmaxf(mx0, s[i]);
-        mx1 = fmaxf(mx1, s[i + 1]);
-        mx2 = fmaxf(mx2, s[i + 2]);
-        mx3 = fmaxf(mx3, s[i + 3]);
+    for (int i = 12; i + 8 <= kTile; i += 8) {
+        mx0 = max3(mx0, s[i], s[i + 1]);
+        mx1 = max3(mx1, s[i + 2], s[i + 3]);
+        mx2 = max3(mx2, s[i + 4], s[i + 5]);
+        mx3 = max3(mx3, s[i + 6], s[i + 7]);
     }
+    // 12 + 8*14 = 124: four elements left
+    mx0 = max3(mx0, s[124], s[125]);
+    mx1 = max3(mx1, s[126], s[127]);
     return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 }
 
 // Running-maximum update of the online softmax.
-//   m      running raw maximum (updated);  mx  maximum of the new score row;  c  log2(e)/sqrt(H)
+//   m      reference maximum that the exponents are taken against (updated)
+//   mx     maximum of the new score row;  c  log2(e)/sqrt(H)
 // Returns alpha, the factor by which everything accumulated before this step must be multiplied,
-// and nmc = -m_new*c, the addend of the folded exponent s*c - m_new*c.
+// and nmc = -m*c, the addend of the folded exponent s*c - m*c.
+// The reference maximum only moves when the new row exceeds it by more than 2^8 in the exp2
+// domain: P then stays below 256 (exact in fp16 to 11 bits like any other magnitude), sum and
+// numerator are fp32, and alpha is exactly 1 on most steps, which lets the O rescale be skipped.
+// The final Y = O / l does not depend on which reference was used.
+constexpr float kLazyRescaleLog2 = 8.f;
 __device__ __forceinline__ float update_max(float& m, const float mx, const float c, float& nmc) {
     const float m_new = fmaxf(m, mx);
-    // A row that has seen nothing but -inf so far (possible only with an additive mask) keeps
-    // p = 0 and l = 0 instead of producing inf - inf.
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = ex2_approx((m - m_use) * c);
+    const bool keep = (m_new - m) * c <= kLazyRescaleLog2;   // false for the first tile (m = -inf)
+    // A row that has seen nothing but -inf so far (possible only with an additive mask) uses 0
+    // as its reference, so that p = 0 and l = 0 instead of inf - inf.
+    const float m_use = keep ? m : ((m_new == -INFINITY) ? 0.f : m_new);
+    const float alpha = keep ? 1.f : ex2_approx((m - m_use) * c);
     nmc = -m_use * c;
-    m = m_new;
+    m = keep ? m : m_new;
     return alpha;
 }
 
@@ -131,21 +166,25 @@ __device__ __forceinline__ float update_max(float& m, const float mx, const floa
 // per column, even key index in the low half); returns the fp32 row sum of P.
 __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const float c,
                                                  const float nmc, const uint32_t tP) {
-    float sum0 = 0.f, sum1 = 0.f;
+    const uint64_t c2 = pack_f32x2(c, c), n2 = pack_f32x2(nmc, nmc);
+    uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const float p0 = ex2_approx(fmaf(s[chunk * 32 + 2 * e], c, nmc));
-            const float p1 = ex2_approx(fmaf(s[chunk * 32 + 2 * e + 1], c, nmc));
-            sum0 += p0;
-            sum1 += p1;
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s[chunk * 32 + 2 * e], s[chunk * 32 + 2 * e + 1]), c2, n2), x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (e & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
+            else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
             pk[e] = pack_half2(p0, p1);
         }
         tmem_st16(tP + chunk * 16, pk);
     }
-    return sum0 + sum1;
+    float lo, hi;
+    unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
+    return lo + hi;
 }
 
 // Read one O row from TMEM, multiply by `f`, write it back.
@@ -362,9 +401,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     enum {
         BAR_Q0 = 0, BAR_Q1,          // TMA -> MMA: query tile landed
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
-        BAR_P0, BAR_P1,              // softmax -> MMA: P tile written (128 arrivals)
+        BAR_P0, BAR_P1,              // softmax + correction -> MMA: P written and O rescaled for
+                                     // this step (256 arrivals: 128 from each warpgroup)
         BAR_PV0, BAR_PV1,            // MMA -> correction: P V of this step complete
-        BAR_OK0, BAR_OK1,            // correction -> MMA: O rescaled for this step (128 arrivals)
         BAR_A0, BAR_A1,              // softmax -> correction: alpha (or final l) in shared memory
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FULL,                    // NS ring barriers TMA -> MMA
@@ -379,8 +418,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __shared__ uint32_t abort_flag;
 
     const uint32_t tid = threadIdx.x;
-    const uint32_t warp = tid >> 5;
-    const uint32_t lane = tid & 31u;
+    const uint32_t warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
     const uint32_t q_pair = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
     const int32_t col0 = static_cast<int32_t>(head * H);
     const uint32_t n_tiles = p.n_kv_tiles;
@@ -395,9 +433,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < BAR_COUNT; ++i) {
-            const bool many = (i == BAR_P0 || i == BAR_P1 || i == BAR_OK0 || i == BAR_OK1 ||
-                               i == BAR_A0 || i == BAR_A1);
-            mbar_init(bar(i), many ? 128u : 1u);
+            const uint32_t count = (i == BAR_P0 || i == BAR_P1) ? 256u
+                                   : (i == BAR_A0 || i == BAR_A1) ? 128u : 1u;
+            mbar_init(bar(i), count);
         }
         abort_flag = 0;
         fence_mbar_init();
@@ -412,21 +450,25 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
 
     if (warp < 8) {
         // ------------------------------------------------------------------ softmax, tile i
-        setmaxnreg_inc<192>();
+        setmaxnreg_inc<184>();
         const uint32_t i = warp >> 2;
         const uint32_t row = tid & 127u;
         const uint32_t tS = tmem_base + (((warp & 3u) * 32u) << 16) + (i ? C::kColS1 : C::kColS0);
         float m = -INFINITY, l = 0.f;
+        FA_TRACE_DECL
+        const bool tr_me = row == 0;
         for (uint32_t j = 0; j < n_tiles; ++j) {
             mbar_wait(bar(BAR_S0 + i), j & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
             tc_fence_after();
             __syncwarp();
+            if (tr_me) FA_TRACE_EV(1 + i, 1);   // S ready
             float s[kTile];
             load_s_row(tS, s);
+            if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
             if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
             // alpha is needed by the correction warps before P is needed by the MMA: publish it
             // first.  It only depends on the row maximum.
@@ -436,10 +478,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 alpha_buf[i][j & 1u][row] = alpha;
                 mbar_arrive(bar(BAR_A0 + i));
             }
+            if (tr_me) FA_TRACE_EV(1 + i, 3);   // alpha published
             l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_P0 + i));
+            if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
         }
         alpha_buf[i][n_tiles & 1u][row] = l;
         mbar_arrive(bar(BAR_A0 + i));
@@ -448,21 +492,29 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         setmaxnreg_dec<64>();
         const uint32_t row = tid & 127u;
         const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
+        FA_TRACE_DECL
+        const bool tr_me = row == 0;
+        // step 0 has nothing to rescale: give the MMA warp its half of the arrivals right away
+        mbar_arrive(bar(BAR_P0));
+        mbar_arrive(bar(BAR_P1));
         for (uint32_t j = 1; j < n_tiles; ++j) {
 #pragma unroll
             for (uint32_t i = 0; i < 2; ++i) {
                 const uint32_t ph = (j - 1) & 1u;
                 mbar_wait(bar(BAR_A0 + i), ph, ctl, kRoleCorrection | (BAR_A0 + i));
                 const float alpha = alpha_buf[i][j & 1u][row];
+                if (tr_me) FA_TRACE_EV(3, 1 + 4 * i);   // alpha seen
                 mbar_wait(bar(BAR_PV0 + i), ph, ctl, kRoleCorrection | (BAR_PV0 + i));
                 tc_fence_after();
                 __syncwarp();
+                if (tr_me) FA_TRACE_EV(3, 2 + 4 * i);   // previous P V done
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
                     rescale_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), alpha);
                     tmem_wait_st();
                 }
                 tc_fence_before();
-                mbar_arrive(bar(BAR_OK0 + i));
+                mbar_arrive(bar(BAR_P0 + i));
+                if (tr_me) FA_TRACE_EV(3, 3 + 4 * i);   // O rescaled
             }
         }
 #pragma unroll
@@ -479,9 +531,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                            q_row < p.L);
         }
     } else {
-        setmaxnreg_dec<64>();
-        if (warp == 12 && lane == 0) {
+        setmaxnreg_dec<80>();
+        if (warp == 12) {
             // -------------------------------------------------------------- MMA issue
+            // The whole warp walks the loop (uniform control flow keeps descriptors in uniform
+            // registers); one elected lane issues the MMAs and commits.
+            const bool leader = elect_one();
             const uint32_t tS0 = tmem_base + C::kColS0, tS1 = tmem_base + C::kColS1;
             const uint32_t tO0 = tmem_base + C::kColO0, tO1 = tmem_base + C::kColO1;
             auto slot_addr = [&](uint32_t t) { return sRing + (t % NS) * G::kTileBytes; };
@@ -489,50 +544,71 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mbar_wait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
             };
             auto free_slot = [&](uint32_t t) { tc_commit(bar(BAR_EMPTY + (t % NS))); };
+#ifdef FA_TRACE
+            uint32_t tr_n = 0;
+            const bool tr_on = leader && p.trace != nullptr &&
+                (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == p.trace_cta;
+#endif
             // ring item 2j is K tile j, item 2j+1 is V tile j
             mbar_wait(bar(BAR_Q0), 0, ctl, kRoleMma | BAR_Q0);
             wait_full(0);
             tc_fence_after();
-            issue_qk<H>(tS0, sQ, slot_addr(0));
-            tc_commit(bar(BAR_S0));
+            if (leader) {
+                issue_qk<H>(tS0, sQ, slot_addr(0));
+                tc_commit(bar(BAR_S0));
+            }
             mbar_wait(bar(BAR_Q1), 0, ctl, kRoleMma | BAR_Q1);
             tc_fence_after();
-            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
-            tc_commit(bar(BAR_S1));
-            free_slot(0);
+            if (leader) {
+                issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
+                tc_commit(bar(BAR_S1));
+                free_slot(0);
+            }
             for (uint32_t j = 0; j < n_tiles; ++j) {
                 const uint32_t tv = 2 * j + 1, tk = 2 * j + 2;
                 const bool more = j + 1 < n_tiles;
                 const uint32_t acc = j > 0 ? 1u : 0u;
+                // both tiles of this step land long before P is ready: take these waits off the path
                 wait_full(tv);
+                if (more) wait_full(tk);
+                FA_TRACE_EV(0, 1);   // V and next K landed
                 // tile 0
                 mbar_wait(bar(BAR_P0), j & 1u, ctl, kRoleMma | BAR_P0);
-                if (j > 0) mbar_wait(bar(BAR_OK0), (j - 1) & 1u, ctl, kRoleMma | BAR_OK0);
+                FA_TRACE_EV(0, 2);   // P0 ready, O0 rescaled
                 tc_fence_after();
-                issue_pv<H>(tO0, tS0, slot_addr(tv), acc);
-                tc_commit(bar(BAR_PV0));
-                if (more) {
-                    wait_full(tk);
-                    tc_fence_after();
-                    issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
-                    tc_commit(bar(BAR_S0));
+                if (leader) {
+                    issue_pv<H>(tO0, tS0, slot_addr(tv), acc);
+                    tc_commit(bar(BAR_PV0));
                 }
+                FA_TRACE_EV(0, 8);   // P V of tile 0 issued
+                if (more) {
+                    if (leader) {
+                        issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
+                        tc_commit(bar(BAR_S0));
+                    }
+                }
+                FA_TRACE_EV(0, 4);   // tile 0 MMAs issued
                 // tile 1
                 mbar_wait(bar(BAR_P1), j & 1u, ctl, kRoleMma | BAR_P1);
-                if (j > 0) mbar_wait(bar(BAR_OK1), (j - 1) & 1u, ctl, kRoleMma | BAR_OK1);
+                FA_TRACE_EV(0, 5);   // P1 ready, O1 rescaled
                 tc_fence_after();
-                issue_pv<H>(tO1, tS1, slot_addr(tv), acc);
-                tc_commit(bar(BAR_PV1));
-                free_slot(tv);
-                if (more) {
+                if (leader) {
+                    issue_pv<H>(tO1, tS1, slot_addr(tv), acc);
+                    tc_commit(bar(BAR_PV1));
+                    free_slot(tv);
+                }
+                FA_TRACE_EV(0, 10);  // P V of tile 1 issued
+                if (more && leader) {
                     issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                     tc_commit(bar(BAR_S1));
                     free_slot(tk);
                 }
+                FA_TRACE_EV(0, 7);   // tile 1 MMAs issued
             }
-            tc_commit(bar(BAR_FINAL));
+            if (leader) tc_commit(bar(BAR_FINAL));
+            __syncwarp();
             mbar_wait(bar(BAR_FINAL), 0, ctl, kRoleMma | BAR_FINAL);
-        } else if (warp == 13 && lane == 0) {
+        } else if (warp == 13 && elect_one()) {
             // -------------------------------------------------------------- TMA producer
             const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
             load_tile<H>(sQ, &tmQ, bar(BAR_Q0), col0, q_row0, batch);
