@@ -109,11 +109,12 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_naive_attention(workload, units_target_s: float, threads: int):
+def cpu_naive_attention(workload, target_s: float, threads: int):
     """Time the naive attention (the reference's CPU path, restated in oracle/) on a bounded sample.
 
-    The sample is whole (batch, head) problems of the workload at its full sequence length:
-    as many heads of batch 0 as fit the time target.  Returns (tflops, seconds, sample text).
+    The sample is whole (batch, head) problems of the workload at its full sequence length: as many
+    heads as one call holds comfortably, repeated until about `target_s` seconds of CPU work have
+    run.  Returns (tflops, seconds, sample text).
     """
     import torch
     from fused_attention_b200.workloads import make_inputs
@@ -122,17 +123,19 @@ def cpu_naive_attention(workload, units_target_s: float, threads: int):
     torch.set_num_threads(threads)
     w = workload
     flops_per_head = 4.0 * w.L * w.L * w.H
-    q, k, v = make_inputs(1, w.L, w.H, w.sigma, w.seed)            # one head to calibrate
-    t0 = time.perf_counter()
-    oracle_attention(q, k, v, w.H)
-    t_one = time.perf_counter() - t0
-    heads = int(max(1, min(w.R * w.B, units_target_s / max(t_one, 1e-6))))
-    heads = min(heads, w.R)
+    heads = max(1, min(w.R, (1 << 28) // (w.L * w.L)))     # scores of one call stay under 1 GiB
     q, k, v = make_inputs(1, w.L, heads * w.H, w.sigma, w.seed)
-    t0 = time.perf_counter()
-    oracle_attention(q, k, v, w.H)
-    dt = time.perf_counter() - t0
-    return heads * flops_per_head / dt / 1e12, dt, f"{heads} of {w.B * w.R} (batch,head) problems of {w.name} at full L={w.L}, fp32"
+    oracle_attention(q, k, v, w.H)                           # warm-up (thread pool, allocator)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        oracle_attention(q, k, v, w.H)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= target_s or reps >= 10000:
+            break
+    text = (f"{reps} x {heads} (batch,head) problems of {w.name} at full L={w.L}, fp32, "
+            f"{dt:.1f} s of CPU work")
+    return reps * heads * flops_per_head / dt / 1e12, dt, text
 
 
 def run_reference(args, workload) -> dict:
@@ -241,10 +244,10 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
         time.sleep(0.0005)
     clocks = sampler.stop()
     barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
     my_ms_per_launch = e0.elapsed_time(e1) / args.steps
-    ms_per_step = ms_total / args.steps
-    value = total_flops / (ms_per_step * 1e-3) / 1e12
+    agg = fa.aggregate_throughput(my_flops * args.steps, e0.elapsed_time(e1) * 1e-3, sum_over_ranks, max_over_ranks)
+    ms_per_step = agg["seconds"] * 1e3 / args.steps
+    value = agg["tflops"]
 
     # end to end: host buffers in, host buffer out, through the host entry point of the C ABI
     hy = torch.empty_like(hq).pin_memory()

@@ -10,9 +10,11 @@ The compute path is the CUDA library ``lib/libfa_b200.so`` behind the C ABI of
 """
 from . import _lib
 from .api import attention_forward, attention_forward_host, query, read_status, select_kernel
-from .sharding import Shard, attention_bytes, attention_flops, shard_units, slice_tensor
+from .sharding import (Shard, aggregate_throughput, attention_bytes, attention_flops, shard_units,
+                       slice_tensor)
 
 __all__ = [
     "attention_forward", "attention_forward_host", "query", "read_status", "select_kernel",
-    "Shard", "shard_units", "slice_tensor", "attention_flops", "attention_bytes", "_lib",
+    "Shard", "shard_units", "slice_tensor", "attention_flops", "attention_bytes", "aggregate_throughput",
+    "_lib",
 ]

@@ -402,9 +402,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_Q0 = 0, BAR_Q1,          // TMA -> MMA: query tile landed
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
         BAR_P0, BAR_P1,              // softmax + correction -> MMA: P written and O rescaled for
-                                     // this step (256 arrivals: 128 from each warpgroup)
+                                     // this step (8 arrivals: one per warp of the two warpgroups)
         BAR_PV0, BAR_PV1,            // MMA -> correction: P V of this step complete
         BAR_A0, BAR_A1,              // softmax -> correction: alpha (or final l) in shared memory
+                                     // (4 arrivals: one per softmax warp)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FULL,                    // NS ring barriers TMA -> MMA
         BAR_EMPTY = BAR_FULL + NS,   // NS ring barriers MMA -> TMA
@@ -419,6 +420,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
+    const uint32_t lane = tid & 31u;
     const uint32_t q_pair = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
     const int32_t col0 = static_cast<int32_t>(head * H);
     const uint32_t n_tiles = p.n_kv_tiles;
@@ -433,8 +435,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < BAR_COUNT; ++i) {
-            const uint32_t count = (i == BAR_P0 || i == BAR_P1) ? 256u
-                                   : (i == BAR_A0 || i == BAR_A1) ? 128u : 1u;
+            // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
+            // shared-memory word serialise
+            const uint32_t count = (i == BAR_P0 || i == BAR_P1) ? 8u
+                                   : (i == BAR_A0 || i == BAR_A1) ? 4u : 1u;
             mbar_init(bar(i), count);
         }
         abort_flag = 0;
@@ -476,17 +480,20 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
             if (j > 0) {
                 alpha_buf[i][j & 1u][row] = alpha;
-                mbar_arrive(bar(BAR_A0 + i));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
             }
             if (tr_me) FA_TRACE_EV(1 + i, 3);   // alpha published
             l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(BAR_P0 + i));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
             if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
         }
         alpha_buf[i][n_tiles & 1u][row] = l;
-        mbar_arrive(bar(BAR_A0 + i));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
     } else if (warp < 12) {
         // ------------------------------------------------------------------ correction + epilogue
         setmaxnreg_dec<64>();
@@ -495,8 +502,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         FA_TRACE_DECL
         const bool tr_me = row == 0;
         // step 0 has nothing to rescale: give the MMA warp its half of the arrivals right away
-        mbar_arrive(bar(BAR_P0));
-        mbar_arrive(bar(BAR_P1));
+        if (lane == 0) {
+            mbar_arrive(bar(BAR_P0));
+            mbar_arrive(bar(BAR_P1));
+        }
         for (uint32_t j = 1; j < n_tiles; ++j) {
 #pragma unroll
             for (uint32_t i = 0; i < 2; ++i) {
@@ -513,7 +522,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     tmem_wait_st();
                 }
                 tc_fence_before();
-                mbar_arrive(bar(BAR_P0 + i));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
                 if (tr_me) FA_TRACE_EV(3, 3 + 4 * i);   // O rescaled
             }
         }

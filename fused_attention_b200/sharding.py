@@ -57,3 +57,16 @@ def attention_flops(B: int, R: int, L: int, H: int) -> float:
 def attention_bytes(B: int, R: int, L: int, H: int) -> float:
     """Compulsory global-memory bytes: read Q, K, V once, write Y once, fp16."""
     return 4.0 * B * L * R * H * 2
+
+
+def aggregate_throughput(my_flops: float, my_seconds: float, all_reduce_sum, all_reduce_max) -> dict:
+    """Whole-job throughput of a sharded run: total FLOPs of all ranks over the slowest rank's time.
+
+    `all_reduce_sum` / `all_reduce_max` take a float and return the reduction over ranks (identity
+    functions for one rank); with torch.distributed they are all_reduce calls on the NCCL (GPU) or
+    gloo (CPU tests) backend.  No other exchange happens: the data path has no collective.
+    """
+    total_flops = all_reduce_sum(float(my_flops))
+    seconds = all_reduce_max(float(my_seconds))
+    return {"total_flops": total_flops, "seconds": seconds,
+            "tflops": total_flops / seconds / 1e12 if seconds > 0 else float("inf")}
