@@ -162,26 +162,49 @@ __device__ __forceinline__ float update_max(float& m, const float mx, const floa
     return alpha;
 }
 
+// Every FA_POLY_MOD-th pair of exponentials goes to the FMA-pipe polynomial instead of the MUFU
+// (0 = never).  The MUFU does 4 lanes per clock per sub-partition, so a 128-wide row costs a warp
+// about 1060 clocks there; moving a quarter of the pairs lets both pipes finish together.
+#ifndef FA_POLY_MOD
+#define FA_POLY_MOD 0
+#endif
+
 // P = exp2(s*c + nmc) for one score row: written as fp16 into 64 TMEM columns at tP (two values
-// per column, even key index in the low half); returns the fp32 row sum of P.
+// per column, even key index in the low half); returns the fp32 row sum of P.  With kWithMax the
+// row maximum of s is computed in the same pass (its instructions fill the gaps the MUFU leaves).
+template <bool kWithMax, bool kPoly>
 __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const float c,
-                                                 const float nmc, const uint32_t tP) {
+                                                 const float nmc, const uint32_t tP, float& mx_out) {
     const uint64_t c2 = pack_f32x2(c, c), n2 = pack_f32x2(nmc, nmc);
     uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(s[chunk * 32 + 2 * e], s[chunk * 32 + 2 * e + 1]), c2, n2), x0, x1);
-            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            const float s0 = s[chunk * 32 + 2 * e], s1 = s[chunk * 32 + 2 * e + 1];
+            float x0, x1, p0, p1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2, n2), x0, x1);
+            if (kPoly && FA_POLY_MOD > 0 && (e % (FA_POLY_MOD > 0 ? FA_POLY_MOD : 1)) == 1) {
+                ex2_poly_x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f), p0, p1);
+            } else {
+                p0 = ex2_approx(x0);
+                p1 = ex2_approx(x1);
+            }
             if (e & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
             else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
             pk[e] = pack_half2(p0, p1);
+            if (kWithMax) {
+                if ((e & 3) == 0) mx0 = max3(mx0, s0, s1);
+                else if ((e & 3) == 1) mx1 = max3(mx1, s0, s1);
+                else if ((e & 3) == 2) mx2 = max3(mx2, s0, s1);
+                else mx3 = max3(mx3, s0, s1);
+            }
         }
         tmem_st16(tP + chunk * 16, pk);
     }
+    if (kWithMax) mx_out = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     float lo, hi;
     unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
     return lo + hi;
@@ -344,7 +367,8 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
         float nmc;
         const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
-        l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
+        float unused_mx;
+        l = l * alpha + exp_and_store_p<false, false>(s, p.scale_log2, nmc, tS, unused_mx);
         if (j > 0) rescale_o_row<H>(tO, alpha);  // PV(j-1) finished: BAR_O was waited below
         tmem_wait_st();
         tc_fence_before();
@@ -389,7 +413,8 @@ struct PipeCfg {
 };
 
 // grid = (ceil(L/256), R, B), block = 512.
-// warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1; 8-11: correction + epilogue;
+// warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1 (each also rescales its O rows in
+// the rare steps whose reference maximum moves); 8-11: epilogue (Y = O / l);
 // 12: MMA issue (one thread) and TMEM owner; 13: TMA producer (one thread); 14-15: idle.
 template <int H>
 __global__ void __launch_bounds__(512, 1)
@@ -401,10 +426,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     enum {
         BAR_Q0 = 0, BAR_Q1,          // TMA -> MMA: query tile landed
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
-        BAR_P0, BAR_P1,              // softmax + correction -> MMA: P written and O rescaled for
-                                     // this step (8 arrivals: one per warp of the two warpgroups)
-        BAR_PV0, BAR_PV1,            // MMA -> correction: P V of this step complete
-        BAR_A0, BAR_A1,              // softmax -> correction: alpha (or final l) in shared memory
+        BAR_P0, BAR_P1,              // softmax -> MMA: P written (and O rescaled in the rare steps
+                                     // that need it); 4 arrivals, one per softmax warp
+        BAR_PV0, BAR_PV1,            // MMA -> softmax (rescale steps) and epilogue: P V complete
+        BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory
                                      // (4 arrivals: one per softmax warp)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FULL,                    // NS ring barriers TMA -> MMA
@@ -414,7 +439,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[BAR_COUNT];
-    __shared__ float alpha_buf[2][2][kTile];  // [tile][step parity][row]
+    __shared__ float l_buf[2][kTile];  // final row sums, softmax -> epilogue
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_flag;
 
@@ -437,8 +462,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < BAR_COUNT; ++i) {
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
-            const uint32_t count = (i == BAR_P0 || i == BAR_P1) ? 8u
-                                   : (i == BAR_A0 || i == BAR_A1) ? 4u : 1u;
+            const uint32_t count = (i == BAR_P0 || i == BAR_P1 || i == BAR_A0 || i == BAR_A1) ? 4u : 1u;
             mbar_init(bar(i), count);
         }
         abort_flag = 0;
@@ -461,7 +485,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         setmaxnreg_inc<184>();
         const uint32_t i = warp >> 2;
         const uint32_t row = tid & 127u;
-        const uint32_t tS = tmem_base + (((warp & 3u) * 32u) << 16) + (i ? C::kColS1 : C::kColS0);
+        const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
+        const uint32_t tS = tmem_base + lane_off + (i ? C::kColS1 : C::kColS0);
+        const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
+        const float c = p.scale_log2;
         float m = -INFINITY, l = 0.f;
         FA_TRACE_DECL
         const bool tr_me = row == 0;
@@ -474,65 +501,54 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             load_s_row(tS, s);
             if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
             if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
-            // alpha is needed by the correction warps before P is needed by the MMA: publish it
-            // first.  It only depends on the row maximum.
-            float nmc;
-            const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
-            if (j > 0) {
-                alpha_buf[i][j & 1u][row] = alpha;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
+            float unused;
+            if (j == 0) {
+                // first key tile: the reference maximum is this tile's row maximum
+                m = row_max(s);
+                l = exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
+            } else {
+                // Later tiles: take the exponentials against the current reference while the row
+                // maximum is computed in the same pass.  The reference only has to move when the new
+                // maximum exceeds it by more than 2^8 in the exp2 domain, which is rare.
+                float mx;
+                const float sum = exp_and_store_p<true, true>(s, c, -m * c, tS, mx);
+                const bool moved = (mx - m) * c > kLazyRescaleLog2;
+                if (__any_sync(0xffffffffu, moved)) {
+                    // Some row of this warp needs a new reference: redo the warp's exponentials
+                    // (rows that keep theirs reproduce the same P) and rescale O by alpha.
+                    const float m_new = moved ? mx : m;
+                    const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
+                    m = m_new;
+                    l = l * alpha + exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
+                    mbar_wait(bar(BAR_PV0 + i), (j - 1) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                    tc_fence_after();
+                    __syncwarp();
+                    rescale_o_row<H>(tO, alpha);
+                } else {
+                    l += sum;
+                }
             }
-            if (tr_me) FA_TRACE_EV(1 + i, 3);   // alpha published
-            l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
             if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
         }
-        alpha_buf[i][n_tiles & 1u][row] = l;
+        l_buf[i][row] = l;
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
     } else if (warp < 12) {
-        // ------------------------------------------------------------------ correction + epilogue
+        // ------------------------------------------------------------------ epilogue: Y = O / l
         setmaxnreg_dec<64>();
         const uint32_t row = tid & 127u;
         const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
-        FA_TRACE_DECL
-        const bool tr_me = row == 0;
-        // step 0 has nothing to rescale: give the MMA warp its half of the arrivals right away
-        if (lane == 0) {
-            mbar_arrive(bar(BAR_P0));
-            mbar_arrive(bar(BAR_P1));
-        }
-        for (uint32_t j = 1; j < n_tiles; ++j) {
-#pragma unroll
-            for (uint32_t i = 0; i < 2; ++i) {
-                const uint32_t ph = (j - 1) & 1u;
-                mbar_wait(bar(BAR_A0 + i), ph, ctl, kRoleCorrection | (BAR_A0 + i));
-                const float alpha = alpha_buf[i][j & 1u][row];
-                if (tr_me) FA_TRACE_EV(3, 1 + 4 * i);   // alpha seen
-                mbar_wait(bar(BAR_PV0 + i), ph, ctl, kRoleCorrection | (BAR_PV0 + i));
-                tc_fence_after();
-                __syncwarp();
-                if (tr_me) FA_TRACE_EV(3, 2 + 4 * i);   // previous P V done
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
-                    rescale_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), alpha);
-                    tmem_wait_st();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
-                if (tr_me) FA_TRACE_EV(3, 3 + 4 * i);   // O rescaled
-            }
-        }
 #pragma unroll
         for (uint32_t i = 0; i < 2; ++i) {
-            const uint32_t ph = (n_tiles - 1) & 1u;
-            mbar_wait(bar(BAR_A0 + i), ph, ctl, kRoleCorrection | (BAR_A0 + i));
-            const float l = alpha_buf[i][n_tiles & 1u][row];
-            mbar_wait(bar(BAR_PV0 + i), ph, ctl, kRoleCorrection | (BAR_PV0 + i));
+            mbar_wait(bar(BAR_A0 + i), 0, ctl, kRoleCorrection | (BAR_A0 + i));
+            const float l = l_buf[i][row];
+            // The last P V of this tile: every earlier phase of this barrier has completed by the
+            // time the softmax warps signalled, so the parity test is unambiguous.
+            mbar_wait(bar(BAR_PV0 + i), (n_tiles - 1) & 1u, ctl, kRoleCorrection | (BAR_PV0 + i));
             tc_fence_after();
             __syncwarp();
             const uint32_t q_row = (q_pair * 2u + i) * kTile + row;

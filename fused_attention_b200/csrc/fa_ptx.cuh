@@ -271,6 +271,31 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// mbarrier arrival worth `count` arrivals.
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+// 2^x for a pair of fp32 values on the FMA and integer pipes (no MUFU): round-to-nearest split
+// x = n + f with f in [-0.5, 0.5] by the 1.5*2^23 trick, a degree-3 minimax polynomial for 2^f
+// (relative error 7.5e-5, below the 4.9e-4 spacing of the fp16 values P is rounded to), and n added
+// into the exponent field.  Inputs must be >= -125 (callers clamp) and are meaningful up to ~126.
+__device__ __forceinline__ void ex2_poly_x2(float x0, float x1, float& p0, float& p1) {
+    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23
+    const uint64_t x2 = pack_f32x2(x0, x1);
+    const uint64_t t2 = add_f32x2(x2, pack_f32x2(kMagic, kMagic));          // low mantissa bits = n
+    const uint64_t n2 = add_f32x2(t2, pack_f32x2(-kMagic, -kMagic));        // n as float
+    const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), x2);          // f = x - n
+    uint64_t q2 = fma_f32x2(f2, pack_f32x2(0.0551716685f, 0.0551716685f), pack_f32x2(0.2426111251f, 0.2426111251f));
+    q2 = fma_f32x2(q2, f2, pack_f32x2(0.6932609677f, 0.6932609677f));
+    q2 = fma_f32x2(q2, f2, pack_f32x2(0.9999280572f, 0.9999280572f));
+    float q0, q1, t0, t1;
+    unpack_f32x2(q2, q0, q1);
+    unpack_f32x2(t2, t0, t1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
