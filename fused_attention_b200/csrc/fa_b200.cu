@@ -110,6 +110,7 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
     }
     if (B == 0 || L == 0 || F == 0 || F % H != 0) return FA_B200_ERR_SHAPE;
     if (B > 65535u || F / H > 65535u || L > (1u << 30)) return FA_B200_ERR_SHAPE;  // grid y/z limits
+    if (static_cast<uint64_t>((L + 255) / 256) * (F / H) * B > 0xFFFFFFFFull) return FA_B200_ERR_SHAPE;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(y);
     if (all & 15u) return FA_B200_ERR_ALIGNMENT;
@@ -160,7 +161,8 @@ int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtens
         if (e != cudaSuccess) return static_cast<int>(e);
         c.attr_done |= (1u << slot);
     }
-    const dim3 grid((p.L + 2 * fa::kTile - 1) / (2 * fa::kTile), p.F / H, p.B);
+    const uint32_t sms = static_cast<uint32_t>(c.sm_count);
+    const dim3 grid(p.n_items < sms ? p.n_items : sms, 1, 1);   // persistent: one CTA per SM
     kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
     return static_cast<int>(cudaGetLastError());
 }
@@ -195,6 +197,9 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.L = L;
                 p.F = F;
                 p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
+                p.R = F / H;
+                p.q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
+                p.n_items = p.q_pairs * p.R * B;
                 p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
                 p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
 #ifdef FA_TRACE

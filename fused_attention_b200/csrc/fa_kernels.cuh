@@ -37,6 +37,9 @@ struct Params {
     uint32_t* status;     // device status word pair, see WaitCtl
     uint32_t B, L, F;
     uint32_t n_kv_tiles;  // ceil(L / 128)
+    uint32_t R;           // heads = F / H
+    uint32_t q_pairs;     // ceil(L / 256): pairs of query tiles per (batch, head)
+    uint32_t n_items;     // q_pairs * R * B: work items of the pipelined kernel
     float scale_log2;     // log2(e) / sqrt(H)
     float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
 #ifdef FA_TRACE
@@ -412,10 +415,22 @@ struct PipeCfg {
     static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 };
 
-// grid = (ceil(L/256), R, B), block = 512.
+// Persistent: grid = min(number of SMs, work items), block = 512.  A work item is one pair of
+// 128-row query tiles of one (batch, head); CTA c takes items c, c + grid, c + 2*grid, ...  Items
+// are numbered query-pair fastest, so the CTAs running at any moment share few heads and their
+// K/V tiles stay in L2.  Every role walks the same item list; the key steps of consecutive items
+// form one continuous sequence of "global steps", so the two-tile ping-pong never drains: while
+// the epilogue warps store item k, the MMA and softmax warps are already in item k+1.
+//
 // warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1 (each also rescales its O rows in
 // the rare steps whose reference maximum moves); 8-11: epilogue (Y = O / l);
-// 12: MMA issue (one thread) and TMEM owner; 13: TMA producer (one thread); 14-15: idle.
+// 12: MMA issue (one elected lane) and TMEM owner; 13: TMA producer (one lane); 14-15: idle.
+//
+// Barrier phases (the parity to wait for is the low bit of the index):
+//   per global step g = k*n + j:  S_i (MMA -> softmax), P_i (softmax -> MMA), PV_i (MMA -> all)
+//   per item k:  QFULL_i (TMA -> MMA), QEMPTY_i (MMA -> TMA), A_i (softmax -> epilogue),
+//                OFREE_i (epilogue -> MMA and softmax)
+//   per ring item t (K0 V0 K1 V1 ... across items):  FULL[t % NS], EMPTY[t % NS]
 template <int H>
 __global__ void __launch_bounds__(512, 1)
 fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -424,13 +439,14 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     using C = PipeCfg<H>;
     constexpr int NS = C::kStages;
     enum {
-        BAR_Q0 = 0, BAR_Q1,          // TMA -> MMA: query tile landed
+        BAR_QFULL0 = 0, BAR_QFULL1,  // TMA -> MMA: query tile landed
+        BAR_QEMPTY0, BAR_QEMPTY1,    // MMA -> TMA: the item's last Q K^T of this tile has retired
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
         BAR_P0, BAR_P1,              // softmax -> MMA: P written (and O rescaled in the rare steps
                                      // that need it); 4 arrivals, one per softmax warp
         BAR_PV0, BAR_PV1,            // MMA -> softmax (rescale steps) and epilogue: P V complete
-        BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory
-                                     // (4 arrivals: one per softmax warp)
+        BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
+        BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FULL,                    // NS ring barriers TMA -> MMA
         BAR_EMPTY = BAR_FULL + NS,   // NS ring barriers MMA -> TMA
@@ -439,16 +455,16 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[BAR_COUNT];
-    __shared__ float l_buf[2][kTile];  // final row sums, softmax -> epilogue
+    __shared__ float l_buf[2][2][kTile];  // [item parity][tile][row] final row sums
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_flag;
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
     const uint32_t lane = tid & 31u;
-    const uint32_t q_pair = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-    const int32_t col0 = static_cast<int32_t>(head * H);
-    const uint32_t n_tiles = p.n_kv_tiles;
+    const uint32_t n = p.n_kv_tiles;
+    const uint32_t n_items = p.n_items;
+    const uint32_t q_pairs = p.q_pairs;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;                   // two tiles
@@ -462,8 +478,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < BAR_COUNT; ++i) {
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
-            const uint32_t count = (i == BAR_P0 || i == BAR_P1 || i == BAR_A0 || i == BAR_A1) ? 4u : 1u;
-            mbar_init(bar(i), count);
+            const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_A0 || i == BAR_A1 ||
+                                   i == BAR_OFREE0 || i == BAR_OFREE1);
+            mbar_init(bar(i), per_warp ? 4u : 1u);
         }
         abort_flag = 0;
         fence_mbar_init();
@@ -489,72 +506,90 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tS = tmem_base + lane_off + (i ? C::kColS1 : C::kColS0);
         const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
         const float c = p.scale_log2;
-        float m = -INFINITY, l = 0.f;
         FA_TRACE_DECL
         const bool tr_me = row == 0;
-        for (uint32_t j = 0; j < n_tiles; ++j) {
-            mbar_wait(bar(BAR_S0 + i), j & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
-            tc_fence_after();
-            __syncwarp();
-            if (tr_me) FA_TRACE_EV(1 + i, 1);   // S ready
-            float s[kTile];
-            load_s_row(tS, s);
-            if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
-            if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
-            float unused;
-            if (j == 0) {
-                // first key tile: the reference maximum is this tile's row maximum
-                m = row_max(s);
-                l = exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
-            } else {
-                // Later tiles: take the exponentials against the current reference while the row
-                // maximum is computed in the same pass.  The reference only has to move when the new
-                // maximum exceeds it by more than 2^8 in the exp2 domain, which is rare.
-                float mx;
-                const float sum = exp_and_store_p<true, true>(s, c, -m * c, tS, mx);
-                const bool moved = (mx - m) * c > kLazyRescaleLog2;
-                if (__any_sync(0xffffffffu, moved)) {
-                    // Some row of this warp needs a new reference: redo the warp's exponentials
-                    // (rows that keep theirs reproduce the same P) and rescale O by alpha.
-                    const float m_new = moved ? mx : m;
-                    const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
-                    m = m_new;
-                    l = l * alpha + exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
-                    mbar_wait(bar(BAR_PV0 + i), (j - 1) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
-                    tc_fence_after();
-                    __syncwarp();
-                    rescale_o_row<H>(tO, alpha);
+        uint32_t g = 0;   // global step
+        uint32_t k = 0;   // item count of this CTA
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
+            float m = -INFINITY, l = 0.f;
+            for (uint32_t j = 0; j < n; ++j, ++g) {
+                mbar_wait(bar(BAR_S0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
+                tc_fence_after();
+                __syncwarp();
+                if (tr_me) FA_TRACE_EV(1 + i, 1);   // S ready
+                float s[kTile];
+                load_s_row(tS, s);
+                if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
+                if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
+                float unused;
+                if (j == 0) {
+                    // first key tile: the reference maximum is this tile's row maximum
+                    m = row_max(s);
+                    l = exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
                 } else {
-                    l += sum;
+                    // Later tiles: take the exponentials against the current reference while the
+                    // row maximum is computed in the same pass.  The reference only has to move
+                    // when the new maximum exceeds it by more than 2^8 in the exp2 domain.
+                    float mx;
+                    const float sum = exp_and_store_p<true, true>(s, c, -m * c, tS, mx);
+                    const bool moved = (mx - m) * c > kLazyRescaleLog2;
+                    if (__any_sync(0xffffffffu, moved)) {
+                        // Some row of this warp needs a new reference: redo the warp's exponentials
+                        // (rows that keep theirs reproduce the same P) and rescale O by alpha.
+                        const float m_new = moved ? mx : m;
+                        const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
+                        m = m_new;
+                        l = l * alpha + exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
+                        mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                        tc_fence_after();
+                        __syncwarp();
+                        rescale_o_row<H>(tO, alpha);
+                    } else {
+                        l += sum;
+                    }
                 }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
+                if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
             }
-            tmem_wait_st();
-            tc_fence_before();
+            // Hand the row sums to the epilogue.  The A barrier may run at most one phase ahead of
+            // the epilogue's wait, so the previous item's O must have been read out first (always
+            // true already when an item has two or more key steps).
+            if (k > 0) mbar_wait(bar(BAR_OFREE0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OFREE0 + i));
+            l_buf[k & 1u][i][row] = l;
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
-            if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
+            if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
         }
-        l_buf[i][row] = l;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
     } else if (warp < 12) {
         // ------------------------------------------------------------------ epilogue: Y = O / l
         setmaxnreg_dec<64>();
         const uint32_t row = tid & 127u;
         const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
+        uint32_t k = 0;
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
+            const uint32_t q_pair = item % q_pairs, bh = item / q_pairs;
+            const uint32_t head = bh % p.R, batch = bh / p.R;
 #pragma unroll
-        for (uint32_t i = 0; i < 2; ++i) {
-            mbar_wait(bar(BAR_A0 + i), 0, ctl, kRoleCorrection | (BAR_A0 + i));
-            const float l = l_buf[i][row];
-            // The last P V of this tile: every earlier phase of this barrier has completed by the
-            // time the softmax warps signalled, so the parity test is unambiguous.
-            mbar_wait(bar(BAR_PV0 + i), (n_tiles - 1) & 1u, ctl, kRoleCorrection | (BAR_PV0 + i));
-            tc_fence_after();
-            __syncwarp();
-            const uint32_t q_row = (q_pair * 2u + i) * kTile + row;
-            __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
-            store_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), 1.f / l, dst,
-                           q_row < p.L);
+            for (uint32_t i = 0; i < 2; ++i) {
+                // this wait lasts for a whole item: poll every 100 ns
+                mbar_wait_relaxed(bar(BAR_A0 + i), k & 1u, ctl, kRoleCorrection | (BAR_A0 + i), 100);
+                const float l = l_buf[k & 1u][i][row];
+                // The item's last P V of this tile.  Every earlier phase of this barrier has
+                // completed by the time the softmax warps signalled and the next phase needs this
+                // epilogue's OFREE arrival, so the parity test is unambiguous.
+                mbar_wait(bar(BAR_PV0 + i), (k * n + n - 1u) & 1u, ctl, kRoleCorrection | (BAR_PV0 + i));
+                tc_fence_after();
+                __syncwarp();
+                const uint32_t q_row = (q_pair * 2u + i) * kTile + row;
+                __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
+                store_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), 1.f / l, dst,
+                               q_row < p.L);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+            }
         }
     } else {
         setmaxnreg_dec<80>();
@@ -572,51 +607,65 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             auto free_slot = [&](uint32_t t) { tc_commit(bar(BAR_EMPTY + (t % NS))); };
 #ifdef FA_TRACE
             uint32_t tr_n = 0;
-            const bool tr_on = leader && p.trace != nullptr &&
-                (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == p.trace_cta;
+            const bool tr_on = leader && p.trace != nullptr && blockIdx.x == p.trace_cta;
 #endif
-            // ring item 2j is K tile j, item 2j+1 is V tile j
-            mbar_wait(bar(BAR_Q0), 0, ctl, kRoleMma | BAR_Q0);
-            wait_full(0);
-            tc_fence_after();
-            if (leader) {
-                issue_qk<H>(tS0, sQ, slot_addr(0));
-                tc_commit(bar(BAR_S0));
+            const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+            const uint32_t steps = my_items * n;   // global steps of this CTA
+            // ring item 2g is the K tile of global step g, item 2g+1 its V tile
+            if (steps > 0) {
+                // S tiles of the very first step
+                mbar_wait(bar(BAR_QFULL0), 0, ctl, kRoleMma | BAR_QFULL0);
+                wait_full(0);
+                tc_fence_after();
+                if (leader) {
+                    issue_qk<H>(tS0, sQ, slot_addr(0));
+                    tc_commit(bar(BAR_S0));
+                    if (n == 1) tc_commit(bar(BAR_QEMPTY0));
+                }
+                mbar_wait(bar(BAR_QFULL1), 0, ctl, kRoleMma | BAR_QFULL1);
+                tc_fence_after();
+                if (leader) {
+                    issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
+                    tc_commit(bar(BAR_S1));
+                    if (n == 1) tc_commit(bar(BAR_QEMPTY1));
+                    free_slot(0);
+                }
             }
-            mbar_wait(bar(BAR_Q1), 0, ctl, kRoleMma | BAR_Q1);
-            tc_fence_after();
-            if (leader) {
-                issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
-                tc_commit(bar(BAR_S1));
-                free_slot(0);
-            }
-            for (uint32_t j = 0; j < n_tiles; ++j) {
-                const uint32_t tv = 2 * j + 1, tk = 2 * j + 2;
-                const bool more = j + 1 < n_tiles;
+            uint32_t k = 0, j = 0;   // item and key step of global step g
+            for (uint32_t g = 0; g < steps; ++g) {
+                const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
+                const bool more = g + 1 < steps;          // a next global step exists
+                const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
                 const uint32_t acc = j > 0 ? 1u : 0u;
-                // both tiles of this step land long before P is ready: take these waits off the path
+                // everything of this step lands long before P is ready: keep these waits off the path
                 wait_full(tv);
-                if (more) wait_full(tk);
+                if (more) {
+                    wait_full(tk);
+                    if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                }
+                if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
                 FA_TRACE_EV(0, 1);   // V and next K landed
                 // tile 0
-                mbar_wait(bar(BAR_P0), j & 1u, ctl, kRoleMma | BAR_P0);
-                FA_TRACE_EV(0, 2);   // P0 ready, O0 rescaled
+                mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                FA_TRACE_EV(0, 2);   // P0 ready
                 tc_fence_after();
                 if (leader) {
                     issue_pv<H>(tO0, tS0, slot_addr(tv), acc);
                     tc_commit(bar(BAR_PV0));
                 }
                 FA_TRACE_EV(0, 8);   // P V of tile 0 issued
-                if (more) {
-                    if (leader) {
-                        issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
-                        tc_commit(bar(BAR_S0));
-                    }
+                if (more && leader) {
+                    issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
+                    tc_commit(bar(BAR_S0));
+                    // the Q K^T of an item's last key step is its last use of the query tile
+                    if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
                 }
                 FA_TRACE_EV(0, 4);   // tile 0 MMAs issued
                 // tile 1
-                mbar_wait(bar(BAR_P1), j & 1u, ctl, kRoleMma | BAR_P1);
-                FA_TRACE_EV(0, 5);   // P1 ready, O1 rescaled
+                if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                FA_TRACE_EV(0, 5);   // P1 ready
                 tc_fence_after();
                 if (leader) {
                     issue_pv<H>(tO1, tS1, slot_addr(tv), acc);
@@ -627,46 +676,56 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (more && leader) {
                     issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                     tc_commit(bar(BAR_S1));
+                    if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
                     free_slot(tk);
                 }
                 FA_TRACE_EV(0, 7);   // tile 1 MMAs issued
+                if (++j == n) { j = 0; ++k; }
             }
             if (leader) tc_commit(bar(BAR_FINAL));
             __syncwarp();
             mbar_wait(bar(BAR_FINAL), 0, ctl, kRoleMma | BAR_FINAL);
         } else if (warp == 13 && elect_one()) {
             // -------------------------------------------------------------- TMA producer
-            const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
-            load_tile<H>(sQ, &tmQ, bar(BAR_Q0), col0, q_row0, batch);
-            uint32_t issued = 0;
-            bool q1_issued = false;
-            const uint32_t total = 2 * n_tiles;
-            for (uint32_t t = 0; t < total; ++t) {
-                if (t == 1) {
-                    load_tile<H>(sQ + G::kTileBytes, &tmQ, bar(BAR_Q1), col0, q_row0 + kTile, batch);
-                    q1_issued = true;
+            uint32_t t = 0;           // ring item
+            uint32_t k = 0;           // item count of this CTA
+            bool stop = false;
+            bool q_pending[2] = {false, false};
+            for (uint32_t item = blockIdx.x; item < n_items && !stop; item += gridDim.x, ++k) {
+                const uint32_t q_pair = item % q_pairs, bh = item / q_pairs;
+                const int32_t col0 = static_cast<int32_t>((bh % p.R) * H);
+                const int32_t batch = static_cast<int32_t>(bh / p.R);
+                const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
+                for (uint32_t tt = 0; tt < 2 * n; ++tt, ++t) {
+                    if (tt < 2) {
+                        // query tile tt of this item, once the previous item has let go of the buffer
+                        if (k > 0 && !mbar_wait(bar(BAR_QEMPTY0 + tt), (k - 1u) & 1u, ctl,
+                                                kRoleProducer | (BAR_QEMPTY0 + tt))) { stop = true; break; }
+                        load_tile<H>(sQ + tt * G::kTileBytes, &tmQ, bar(BAR_QFULL0 + tt), col0,
+                                     q_row0 + static_cast<int32_t>(tt * kTile), batch);
+                        q_pending[tt] = true;
+                    }
+                    const uint32_t slot = t % NS;
+                    if (!mbar_wait(bar(BAR_EMPTY + slot), ((t / NS) & 1u) ^ 1u, ctl,
+                                   kRoleProducer | (BAR_EMPTY + slot))) { stop = true; break; }
+                    load_tile<H>(sRing + slot * G::kTileBytes, (tt & 1u) ? &tmV : &tmK, bar(BAR_FULL + slot),
+                                 col0, static_cast<int32_t>((tt >> 1) * kTile), batch);
                 }
-                const uint32_t slot = t % NS;
-                const bool ok = mbar_wait(bar(BAR_EMPTY + slot), ((t / NS) & 1u) ^ 1u, ctl,
-                                          kRoleProducer | (BAR_EMPTY + slot));
-                if (!ok) break;  // a wait expired somewhere: issue nothing more
-                load_tile<H>(sRing + slot * G::kTileBytes, (t & 1u) ? &tmV : &tmK, bar(BAR_FULL + slot),
-                             col0, static_cast<int32_t>((t >> 1) * kTile), batch);
-                issued = t + 1;
             }
             if (abort_flag != 0u) {
                 // Do not leave the CTA while one of its own copies may still be landing.
-                const uint32_t first = issued > NS ? issued - NS : 0u;
-                for (uint32_t t = first; t < issued; ++t) {
-                    const uint32_t slot = t % NS;
+                const uint32_t first = t > NS ? t - NS : 0u;
+                for (uint32_t u = first; u < t; ++u) {
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(bar(BAR_FULL + slot), (t / NS) & 1u) &&
+                    while (!mbar_try_wait(bar(BAR_FULL + (u % NS)), (u / NS) & 1u) &&
                            clock64() - t0 < 200000000LL) {
                     }
                 }
-                const long long t0 = clock64();
-                while (!(mbar_try_wait(bar(BAR_Q0), 0) && (!q1_issued || mbar_try_wait(bar(BAR_Q1), 0))) &&
-                       clock64() - t0 < 200000000LL) {
+                for (uint32_t tt = 0; tt < 2; ++tt) {
+                    const long long t0 = clock64();
+                    while (q_pending[tt] && !mbar_try_wait(bar(BAR_QFULL0 + tt), (k > 0 ? k - 1u : 0u) & 1u) &&
+                           clock64() - t0 < 200000000LL) {
+                    }
                 }
             }
         }

@@ -27,6 +27,26 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Named barrier over `n` threads (a multiple of 32) of the CTA; ids 1..15 (0 is __syncthreads).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t n) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+// Same barrier, returning the OR of `pred` over all participating threads.
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t n, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(r)
+        : "r"(id), "r"(n), "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return r != 0;
+}
+
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -79,6 +99,25 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Wa
                 }
                 return false;
             }
+        }
+    }
+    return true;
+}
+
+// Same wait for roles that are far from the critical path: sleeps between polls so that the
+// polling warp leaves the issue slots of its sub-partition to the warps that are computing.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, WaitCtl ctl,
+                                                  uint32_t code, uint32_t sleep_ns) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(sleep_ns);
+        if (*ctl.abort_flag != 0u) return false;
+        if (clock64() - t0 > ctl.cap_cycles) {
+            if (atomicExch(const_cast<uint32_t*>(ctl.abort_flag), 1u) == 0u) {
+                atomicCAS(ctl.status, 0u, code);
+                atomicAdd(ctl.status + 1, 1u);
+            }
+            return false;
         }
     }
     return true;
@@ -230,7 +269,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
         "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
         "r"(v[15])
-        : "memory");
+#ifndef FA_ST_NOCLOBBER
+        : "memory"
+#endif
+        );
 }
 
 // ----------------------------------------------------------------------------- arithmetic
@@ -260,6 +302,7 @@ __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
 __device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
+#ifndef FA_SCALAR_MATH
 __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
@@ -270,6 +313,18 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+#else  // comparison build: the same interface on scalar instructions
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    float a0, a1, b0, b1, c0, c1;
+    unpack_f32x2(a, a0, a1); unpack_f32x2(b, b0, b1); unpack_f32x2(c, c0, c1);
+    return pack_f32x2(fmaf(a0, b0, c0), fmaf(a1, b1, c1));
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    float a0, a1, b0, b1;
+    unpack_f32x2(a, a0, a1); unpack_f32x2(b, b0, b1);
+    return pack_f32x2(a0 + b0, a1 + b1);
+}
+#endif
 
 // mbarrier arrival worth `count` arrivals.
 __device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
