@@ -263,12 +263,21 @@ def _run_ref_wmma(lib, q, k, v, H, C):
                                  (64, 128), (128, 32), (128, 64), (128, 128)])
 def test_against_the_reference_fused_kernel_on_its_own_test_shapes(H, C):
     """The reference's WMMA kernel (compiled for sm_100a from its own header) on the shapes its
-    unit tests use (B=1, R=2, L=2*C), compared at the reference's tolerance rtol=atol=1e-2."""
+    unit tests use (B=1, R=2, L=2*C).  Where the reference kernel itself is within 5e-3 of the fp32
+    oracle the two kernels must agree at the reference's tolerance rtol=atol=1e-2; where it is not
+    (its fp16 accumulation and its unsynchronised shared-memory alias make some instances drift on
+    this GPU) this implementation must still be the closer one."""
     lib = _ref_wmma()
-    q, k, v = (t.cuda() for t in make_inputs(1, 2 * C, 2 * H, 1.0, 179))
+    hq, hk, hv = make_inputs(1, 2 * C, 2 * H, 1.0, 179)
+    q, k, v = hq.cuda(), hk.cuda(), hv.cuda()
+    expected = oracle(hq, hk, hv, H)
     y_ref = _run_ref_wmma(lib, q, k, v, H, C)
     y = fa.attention_forward(H, C, q, k, v)
-    torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
+    err_new = assert_close(y.float().cpu(), expected)
+    err_ref = error_metrics(y_ref.float().cpu(), expected)
+    if err_ref["max_abs"] <= 5e-3:
+        torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
+    assert err_new["max_abs"] <= err_ref["max_abs"], (err_new, err_ref)
 
 
 @pytest.mark.parametrize("H,C,B,R,L", [(64, 64, 1, 4, 256), (128, 128, 2, 4, 512), (64, 128, 8, 12, 512)])
