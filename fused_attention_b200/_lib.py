@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libfa_b200.so")
 EXPORTED_SYMBOLS = (
     "fa_b200_attention_forward",
     "fa_b200_attention_forward_host",
+    "fa_b200_attention_forward_noalloc",
     "fa_b200_strerror",
     "fa_b200_query",
     "fa_b200_read_status",
@@ -64,6 +65,8 @@ def load() -> ctypes.CDLL:
         u32, vp, i32 = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
         lib.fa_b200_attention_forward.restype = i32
         lib.fa_b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
+        lib.fa_b200_attention_forward_noalloc.restype = i32
+        lib.fa_b200_attention_forward_noalloc.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
         lib.fa_b200_attention_forward_host.restype = i32
         lib.fa_b200_attention_forward_host.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, u32]
         lib.fa_b200_strerror.restype = ctypes.c_char_p

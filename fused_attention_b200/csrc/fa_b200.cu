@@ -254,9 +254,148 @@ int grow(DeviceCtx& c, int i, size_t bytes) {
     return FA_B200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch of the no-allocation entry point: one status pair {failure code, count} per CTA of the
+// one-tile-per-CTA kernel.  File-scope device memory: every GPU that loads this library holds these
+// 128 KiB until the process exits.  In host code the name `g_noalloc_status` is only a handle for
+// cudaGetSymbolAddress; the kernel must be given the address that call returns.
+constexpr uint32_t kNoAllocMaxCtas = 16384;
+static __device__ __align__(256) uint32_t g_noalloc_status[2 * kNoAllocMaxCtas];
+
+struct NoAllocCtx {
+    bool ready = false;
+    int cc_major = 0;
+    uint32_t* status_dev = nullptr;  // device address of g_noalloc_status on this device
+    uint32_t attr_done = 0;
+};
+NoAllocCtx g_noalloc[kMaxDevices];
+
+template <int H, bool M>
+int launch_simple_noalloc(NoAllocCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
+                          const CUtensorMap& mv, const Params& p, dim3 grid, cudaStream_t st) {
+    constexpr int smem = 3 * fa::TileGeom<H>::kTileBytes + 1024;
+    auto kern = fa::fa_fwd_simple<H, M, true>;
+    if (!(c.attr_done & (1u << slot))) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.attr_done |= (1u << slot);
+    }
+    kern<<<grid, 128, smem, st>>>(mq, mk, mv, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace
 
 extern "C" {
+
+int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* v, const void* mask_or_null,
+                                      void* y, uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
+                                      uint32_t chunk_hint, int device, void* cuda_stream, uint32_t flags) {
+    if (flags & ~static_cast<uint32_t>(FA_B200_FLAG_SYNC)) return FA_B200_ERR_FLAGS;  // one kernel: nothing to force
+    int rc = validate(q, k, v, mask_or_null, y, B, L, F, head_dim, chunk_hint, flags);
+    if (rc != FA_B200_OK) return rc;
+    const uint32_t H = head_dim;
+    const dim3 grid((L + fa::kTile - 1) / fa::kTile, F / H, B);
+    const uint64_t ctas = static_cast<uint64_t>(grid.x) * grid.y * grid.z;
+    if (ctas > kNoAllocMaxCtas) return FA_B200_ERR_TOO_LARGE;
+    if (device < 0 || device >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    NoAllocCtx& c = g_noalloc[device];
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!c.ready) {
+            // Set-up, once per device, with that device current: compute capability, the device
+            // address of the file-scope scratch, the driver's tensor-map encoder.  No allocation.
+            int major = 0;
+            e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+            void* sym = nullptr;
+            if (e == cudaSuccess) e = cudaGetSymbolAddress(&sym, g_noalloc_status);
+            if (e != cudaSuccess) {
+                rc = static_cast<int>(e);
+            } else {
+                c.cc_major = major;
+                c.status_dev = static_cast<uint32_t*>(sym);
+                c.ready = true;
+            }
+        }
+        if (rc == FA_B200_OK && g_encode == nullptr) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+            if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+                (void)cudaGetLastError();
+                rc = FA_B200_ERR_DRIVER;
+            } else {
+                g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            }
+        }
+        if (rc == FA_B200_OK && c.cc_major != 10) rc = FA_B200_ERR_ARCH;
+        CUtensorMap mq, mk, mv;
+        if (rc == FA_B200_OK) rc = make_map(&mq, q, B, L, F, H);
+        if (rc == FA_B200_OK) rc = make_map(&mk, k, B, L, F, H);
+        if (rc == FA_B200_OK) rc = make_map(&mv, v, B, L, F, H);
+        if (rc == FA_B200_OK) {
+            // The array keeps what the previous call left: zero the pairs this grid will use, in
+            // stream order ahead of the kernel.
+            e = cudaMemsetAsync(c.status_dev, 0, static_cast<size_t>(ctas) * 2 * sizeof(uint32_t), st);
+            if (e != cudaSuccess) rc = static_cast<int>(e);
+        }
+        if (rc == FA_B200_OK) {
+            Params p;
+            p.y = static_cast<__half*>(y);
+            p.mask = static_cast<const __half*>(mask_or_null);
+            p.status = c.status_dev;   // the address from cudaGetSymbolAddress, never the symbol itself
+            p.B = B;
+            p.L = L;
+            p.F = F;
+            p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
+            p.R = F / H;
+            p.q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
+            p.n_items = p.q_pairs * p.R * B;
+            p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
+            p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+#ifdef FA_TRACE
+            p.trace = nullptr;
+            p.trace_cta = 0;
+#endif
+            if (mask_or_null) {
+                switch (H) {
+                    case 16: rc = launch_simple_noalloc<16, true>(c, 4, mq, mk, mv, p, grid, st); break;
+                    case 32: rc = launch_simple_noalloc<32, true>(c, 5, mq, mk, mv, p, grid, st); break;
+                    case 64: rc = launch_simple_noalloc<64, true>(c, 6, mq, mk, mv, p, grid, st); break;
+                    default: rc = launch_simple_noalloc<128, true>(c, 7, mq, mk, mv, p, grid, st); break;
+                }
+            } else {
+                switch (H) {
+                    case 16: rc = launch_simple_noalloc<16, false>(c, 0, mq, mk, mv, p, grid, st); break;
+                    case 32: rc = launch_simple_noalloc<32, false>(c, 1, mq, mk, mv, p, grid, st); break;
+                    case 64: rc = launch_simple_noalloc<64, false>(c, 2, mq, mk, mv, p, grid, st); break;
+                    default: rc = launch_simple_noalloc<128, false>(c, 3, mq, mk, mv, p, grid, st); break;
+                }
+            }
+        }
+    }
+    if (rc == FA_B200_OK && (flags & FA_B200_FLAG_SYNC)) {
+        e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) rc = static_cast<int>(e);
+        // read the status pairs back through a fixed buffer on the stack
+        uint32_t buf[512];
+        for (uint64_t off = 0; rc == FA_B200_OK && off < ctas * 2; off += 512) {
+            const size_t cnt = static_cast<size_t>(ctas * 2 - off < 512 ? ctas * 2 - off : 512);
+            e = cudaMemcpy(buf, c.status_dev + off, cnt * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) { rc = static_cast<int>(e); break; }
+            for (size_t i = 0; i < cnt; i += 2)
+                if (buf[i] != 0) { rc = FA_B200_ERR_DEVICE_TIMEOUT; break; }
+        }
+    }
+    if (prev != device) (void)cudaSetDevice(prev);
+    return rc;
+}
 
 int fa_b200_attention_forward(const void* q, const void* k, const void* v, const void* mask_or_null,
                               void* y, uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,

@@ -281,7 +281,9 @@ __device__ __forceinline__ void mask_tail(float (&s)[kTile], int valid) {
 
 // ============================================================================ simple kernel
 // grid = (ceil(L/128), R, B), block = 128.  Thread t owns query row t of the tile (TMEM lane t).
-template <int H, bool kHasMask>
+// kPerCtaStatus (only the no-allocation entry point sets it): p.status is an array of one status
+// pair per CTA instead of one pair per device, so no atomics from different CTAs meet.
+template <int H, bool kHasMask, bool kPerCtaStatus = false>
 __global__ void __launch_bounds__(128)
 fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const Params p) {
@@ -304,7 +306,10 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t sQ = smem_base, sK = sQ + G::kTileBytes, sV = sK + G::kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles};
+    const WaitCtl ctl{kPerCtaStatus
+                          ? p.status + 2u * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
+                          : p.status,
+                      &abort_flag, kWaitCapCycles};
 
     if (tid == 0) {
 #pragma unroll

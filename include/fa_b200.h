@@ -82,6 +82,37 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v,
                                    int device, uint32_t flags);
 
 /*
+ * The same operator for callers that must not allocate.  It has no counterpart in the reference
+ * (whose binding always allocates its output and whose launcher has no workspace at all).
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits or unwanted: inside a region that a
+ * framework is recording for later replay, in a process whose device memory is entirely owned by
+ * another allocator or already handed out, in a latency-critical loop where an allocation would
+ * synchronise the device.  fa_b200_attention_forward allocates (once per device) a small status
+ * buffer for its kernels; this entry point never calls cudaMalloc, cudaFree or any allocating
+ * library routine.
+ *
+ * How: it always runs the one-tile-per-CTA kernel, and that kernel's only scratch (a pair of
+ * status words per CTA, written when a bounded device-side wait expires) lives in a fixed array
+ * inside the library's device image: 16384 pairs = 128 KiB, held by every GPU that loads the
+ * library until the process exits.  Consequences:
+ *   - ceil(L/128) * (F/head_dim) * B must not exceed 16384 CTAs, otherwise the call is rejected
+ *     with FA_B200_ERR_TOO_LARGE before anything is launched;
+ *   - all calls on a device share that array.  Each call zeroes the pairs it is going to use (in
+ *     stream order, ahead of its kernel) and the array otherwise keeps what the last call left;
+ *     two calls whose kernels overlap on the GPU (different streams) race on it, so serialise them;
+ *   - the first call on a device looks up the array's device address and sets the kernel's
+ *     shared-memory attribute; make that first call outside any stream capture.
+ * flags: 0 or FA_B200_FLAG_SYNC (synchronise the stream and return FA_B200_ERR_DEVICE_TIMEOUT if
+ * any CTA reported).  Inputs, outputs, head_dim, chunk_hint, mask: as fa_b200_attention_forward.
+ */
+int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* v,
+                                      const void* mask_or_null, void* y,
+                                      uint32_t B, uint32_t L, uint32_t F,
+                                      uint32_t head_dim, uint32_t chunk_hint,
+                                      int device, void* cuda_stream, uint32_t flags);
+
+/*
  * Human-readable text for a status code returned by this library (negative codes) or by the
  * CUDA runtime (positive codes).  Replaces the stderr printing of the reference's
  * checkCudaError / checkLastCudaError (include/fused_attn.cuh:17-42).
