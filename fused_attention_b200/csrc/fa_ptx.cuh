@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no multicast), tcgen05 (TMEM alloc, MMA, ld/st, commit).
+// mbarrier, TMA (cp.async.bulk.tensor, each CTA fetching its own tiles), tcgen05 (TMEM alloc, MMA, ld/st, commit).
 // Nothing here is specific to attention.
 #pragma once
 
