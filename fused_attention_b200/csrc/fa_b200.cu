@@ -22,14 +22,17 @@ namespace {
 using fa::Params;
 
 constexpr int kMaxDevices = 64;
+constexpr int kHostChunks = 8;   // pipeline depth of the host-buffer entry point
 
 struct DeviceCtx {
     bool ready = false;
     int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
     uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count}
     uint32_t attr_done = 0;       // bit per kernel instance whose smem attribute is set
-    // host-buffer entry point: one stream and grow-on-demand staging buffers
-    cudaStream_t host_stream = nullptr;
+    // host-buffer entry point: copy-in / compute / copy-out streams, per-chunk events and
+    // grow-on-demand staging buffers
+    cudaStream_t host_stream = nullptr, host_stream2 = nullptr, host_stream3 = nullptr;
+    cudaEvent_t ev_in[8] = {}, ev_cmp[8] = {};
     void* stage[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v y mask
     size_t stage_bytes[5] = {0, 0, 0, 0, 0};
 };
@@ -430,31 +433,96 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
         rc = ensure_ctx(device, &c);
         if (rc == FA_B200_OK && c->host_stream == nullptr) {
             e = cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking);
+            if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->host_stream2, cudaStreamNonBlocking);
+            if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->host_stream3, cudaStreamNonBlocking);
+            for (int i = 0; i < kHostChunks && e == cudaSuccess; ++i) {
+                e = cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming);
+                if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_cmp[i], cudaEventDisableTiming);
+            }
             if (e != cudaSuccess) rc = static_cast<int>(e);
         }
         for (int i = 0; i < 4 && rc == FA_B200_OK; ++i) rc = grow(*c, i, bytes);
         if (rc == FA_B200_OK && mbytes) rc = grow(*c, 4, mbytes);
     }
     if (rc == FA_B200_OK) {
-        cudaStream_t st = c->host_stream;
-        const void* src[3] = {q, k, v};
-        for (int i = 0; i < 3 && rc == FA_B200_OK; ++i) {
-            e = cudaMemcpyAsync(c->stage[i], src[i], bytes, cudaMemcpyHostToDevice, st);
+        // Chunked pipeline over three streams: while chunk c computes, chunk c+1 is copied in and
+        // chunk c-1 is copied out (PCIe carries both directions at once).  Chunks are groups of
+        // batch entries (contiguous in host memory) when B >= 2, otherwise groups of heads moved
+        // with pitched copies into compact [B, L, heads*H] device slices.
+        cudaStream_t s_in = c->host_stream, s_cmp = c->host_stream2, s_out = c->host_stream3;
+        const uint32_t H = head_dim, R = F / H;
+        const bool by_batch = B >= 2;
+        const uint32_t units = by_batch ? B : R;
+        const uint32_t n_chunks = units < kHostChunks ? units : kHostChunks;
+        const __half* hsrc[3] = {static_cast<const __half*>(q), static_cast<const __half*>(k),
+                                 static_cast<const __half*>(v)};
+        // every chunk runs the kernel the whole problem would get, so the result has the same
+        // bits as one device-pointer call on the full tensors
+        const uint32_t chunk_flags =
+            (flags & ~static_cast<uint32_t>(FA_B200_FLAG_SYNC | FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED)) |
+            (select_kernel(B, L, F, H, mask_or_null != nullptr, flags, c->sm_count) == 2 ? FA_B200_FLAG_FORCE_PIPELINED
+                                                                                       : FA_B200_FLAG_FORCE_SIMPLE);
+        if (mbytes && !by_batch) {   // the mask is shared by all heads: one copy ahead of everything
+            e = cudaMemcpyAsync(c->stage[4], mask_or_null, mbytes, cudaMemcpyHostToDevice, s_in);
             if (e != cudaSuccess) rc = static_cast<int>(e);
         }
-        if (rc == FA_B200_OK && mbytes) {
-            e = cudaMemcpyAsync(c->stage[4], mask_or_null, mbytes, cudaMemcpyHostToDevice, st);
-            if (e != cudaSuccess) rc = static_cast<int>(e);
+        size_t dev_off = 0;   // elements into the staging buffers
+        for (uint32_t ch = 0; ch < n_chunks && rc == FA_B200_OK; ++ch) {
+            const uint32_t u0 = static_cast<uint32_t>(static_cast<uint64_t>(units) * ch / n_chunks);
+            const uint32_t u1 = static_cast<uint32_t>(static_cast<uint64_t>(units) * (ch + 1) / n_chunks);
+            const uint32_t nu = u1 - u0;
+            if (nu == 0) continue;
+            const uint32_t cB = by_batch ? nu : B, cF = by_batch ? F : nu * H;
+            const size_t elems = static_cast<size_t>(cB) * L * cF;
+            __half* d[4];
+            for (int i = 0; i < 4; ++i) d[i] = static_cast<__half*>(c->stage[i]) + dev_off;
+            const __half* dmask = nullptr;
+            for (int i = 0; i < 3 && rc == FA_B200_OK; ++i) {
+                if (by_batch)
+                    e = cudaMemcpyAsync(d[i], hsrc[i] + static_cast<size_t>(u0) * L * F, elems * sizeof(__half),
+                                        cudaMemcpyHostToDevice, s_in);
+                else
+                    e = cudaMemcpy2DAsync(d[i], static_cast<size_t>(cF) * sizeof(__half), hsrc[i] + static_cast<size_t>(u0) * H,
+                                          static_cast<size_t>(F) * sizeof(__half), static_cast<size_t>(cF) * sizeof(__half),
+                                          static_cast<size_t>(B) * L, cudaMemcpyHostToDevice, s_in);
+                if (e != cudaSuccess) rc = static_cast<int>(e);
+            }
+            if (rc == FA_B200_OK && mbytes) {
+                if (by_batch) {
+                    const size_t moff = static_cast<size_t>(u0) * L * L;
+                    e = cudaMemcpyAsync(static_cast<__half*>(c->stage[4]) + moff,
+                                        static_cast<const __half*>(mask_or_null) + moff,
+                                        static_cast<size_t>(nu) * L * L * sizeof(__half), cudaMemcpyHostToDevice, s_in);
+                    if (e != cudaSuccess) rc = static_cast<int>(e);
+                    dmask = static_cast<const __half*>(c->stage[4]) + moff;
+                } else {
+                    dmask = static_cast<const __half*>(c->stage[4]);
+                }
+            }
+            if (rc == FA_B200_OK && (e = cudaEventRecord(c->ev_in[ch], s_in)) != cudaSuccess) rc = static_cast<int>(e);
+            if (rc == FA_B200_OK && (e = cudaStreamWaitEvent(s_cmp, c->ev_in[ch], 0)) != cudaSuccess) rc = static_cast<int>(e);
+            if (rc == FA_B200_OK)
+                rc = forward_device(d[0], d[1], d[2], dmask, d[3], cB, L, cF, head_dim, device, s_cmp, chunk_flags);
+            if (rc == FA_B200_OK && (e = cudaEventRecord(c->ev_cmp[ch], s_cmp)) != cudaSuccess) rc = static_cast<int>(e);
+            if (rc == FA_B200_OK && (e = cudaStreamWaitEvent(s_out, c->ev_cmp[ch], 0)) != cudaSuccess) rc = static_cast<int>(e);
+            if (rc == FA_B200_OK) {
+                __half* hy = static_cast<__half*>(y);
+                if (by_batch)
+                    e = cudaMemcpyAsync(hy + static_cast<size_t>(u0) * L * F, d[3], elems * sizeof(__half),
+                                        cudaMemcpyDeviceToHost, s_out);
+                else
+                    e = cudaMemcpy2DAsync(hy + static_cast<size_t>(u0) * H, static_cast<size_t>(F) * sizeof(__half), d[3],
+                                          static_cast<size_t>(cF) * sizeof(__half), static_cast<size_t>(cF) * sizeof(__half),
+                                          static_cast<size_t>(B) * L, cudaMemcpyDeviceToHost, s_out);
+                if (e != cudaSuccess) rc = static_cast<int>(e);
+            }
+            dev_off += elems;
         }
-        if (rc == FA_B200_OK)
-            rc = forward_device(c->stage[0], c->stage[1], c->stage[2], mbytes ? c->stage[4] : nullptr,
-                                c->stage[3], B, L, F, head_dim, device, st, flags & ~FA_B200_FLAG_SYNC);
-        if (rc == FA_B200_OK) {
-            e = cudaMemcpyAsync(y, c->stage[3], bytes, cudaMemcpyDeviceToHost, st);
-            if (e != cudaSuccess) rc = static_cast<int>(e);
-        }
-        e = cudaStreamSynchronize(st);
-        if (rc == FA_B200_OK && e != cudaSuccess) rc = static_cast<int>(e);
+        // all three streams drain before the staging buffers may be reused or the result read
+        cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s_cmp), e3 = cudaStreamSynchronize(s_out);
+        if (rc == FA_B200_OK && e1 != cudaSuccess) rc = static_cast<int>(e1);
+        if (rc == FA_B200_OK && e2 != cudaSuccess) rc = static_cast<int>(e2);
+        if (rc == FA_B200_OK && e3 != cudaSuccess) rc = static_cast<int>(e3);
         if (rc == FA_B200_OK) {
             uint32_t w[2] = {0, 0};
             e = cudaMemcpy(w, c->status, sizeof(w), cudaMemcpyDeviceToHost);

@@ -70,8 +70,11 @@ int fa_b200_attention_forward(const void* q, const void* k, const void* v,
 
 /*
  * Same operator with HOST buffers: copies q, k, v (and mask) to the device, runs the kernel and
- * copies y back, all on one internal stream, and returns when y is complete.  The device
- * staging buffers are cached per device and grow on demand.  This is the call a torch-free
+ * copies y back, and returns when y is complete.  The work is cut into up to 8 chunks (batch
+ * entries, or heads when B = 1) that flow through three internal streams, so the copy-in of one
+ * chunk, the kernel of the previous and the copy-out of the one before overlap; pinned host
+ * buffers are needed for that overlap.  Device staging buffers are cached per device and grow on
+ * demand.  This is the call a torch-free
  * host program makes; it plays the role of the reference's standalone driver
  * (src/test.cu:43-62: cudaMalloc, fill, launch, synchronise).
  */

@@ -171,6 +171,15 @@ def test_host_buffer_entry_point_matches_device_entry_point():
     mask[:, :, 250:] = float("-inf")
     y_host_m = fa.attention_forward_host(128, 128, q, k, v, mask).float()
     assert torch.equal(run(q, k, v, 128, mask=mask), y_host_m)
+    # B = 1: the chunks are groups of heads moved with pitched copies
+    q1, k1, v1 = make_inputs(1, 600, 5 * 128, 1.0, 22)
+    assert torch.equal(run(q1, k1, v1, 128), fa.attention_forward_host(128, 128, q1, k1, v1).float())
+    m1 = torch.zeros(1, 600, 600, dtype=torch.float16)
+    m1[:, :, 500:] = float("-inf")
+    assert torch.equal(run(q1, k1, v1, 128, mask=m1), fa.attention_forward_host(128, 128, q1, k1, v1, m1).float())
+    # many batch entries: more entries than chunks
+    q2, k2, v2 = make_inputs(11, 130, 64, 1.0, 23)
+    assert torch.equal(run(q2, k2, v2, 32), fa.attention_forward_host(32, 32, q2, k2, v2).float())
 
 
 def test_non_default_stream_and_output_placement():
