@@ -7,9 +7,10 @@
 A step is one forward pass of the operator over one batch of seeded synthetic input.  The default
 workload is the headline configuration (LLaMA-7B-shaped prefill, B=4 R=32 L=2048 H=128, fp16).
 With N > 1 (one process per GPU; start it under torch.distributed.run, or let this script do so)
-the (batch x head) units are split across the ranks with no collective in the data path
-(`--scaling strong`, the default: the fixed job is divided; `--scaling weak`: every rank runs the
-whole job).  Rank 0 prints ONE JSON line.
+the job is sharded by head across the ranks with no collective in the data path.  `--scaling weak`
+(the default): the job has R*N heads, so every rank holds the workload's own R heads and the work
+per GPU is fixed.  `--scaling strong`: the one workload is divided, R/N heads per rank.
+Rank 0 prints ONE JSON line.
 
 The line carries the device-resident throughput (`value`), the end-to-end throughput through the
 host-buffer entry point with the host<->device copies inside the timed region (`e2e`), the tensor
@@ -210,13 +211,17 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    if args.scaling == "weak" or world == 1:
-        shard = fa.Shard(0, w.B, 0, w.R)
+    strong = args.scaling == "strong"
+    if not strong or world == 1:
+        shard = fa.Shard(0, w.B, 0, w.R)   # weak: the job has R * world heads, R of them here
     else:
         shard = fa.shard_units(w.B, w.R, world, rank)
     my_flops = fa.attention_flops(shard.b1 - shard.b0, shard.h1 - shard.h0, w.L, w.H)
     total_flops = sum_over_ranks(my_flops)
-    hq, hk, hv = workload_inputs(w, heads=slice(shard.h0, shard.h1), batches=slice(shard.b0, shard.b1), pin=True)
+    # weak scaling: rank r holds heads [r*R, (r+1)*R) of the N-times wider job, drawn with its own seed
+    import dataclasses
+    w_rank = w if (strong or world == 1) else dataclasses.replace(w, seed=w.seed + 1000 * rank)
+    hq, hk, hv = workload_inputs(w_rank, heads=slice(shard.h0, shard.h1), batches=slice(shard.b0, shard.b1), pin=True)
     shard_bytes = 4 * hq.numel() * 2
     # Rotate over copies of the inputs so that consecutive steps do not find them in L2.
     nbuf = max(2, math.ceil(4 * L2_BYTES / shard_bytes))
@@ -273,10 +278,12 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
         out = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak" if (args.scaling == "weak" and world > 1) else "strong", "vs_baseline": None,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": w.name, "B": w.B, "R": w.R, "L": w.L, "H": w.H, "sigma": w.sigma,
-                       "seed": w.seed, "sharding": f"(batch x head) units, {shard.units} of {w.B * w.R} on rank 0",
+            "config": {"workload": w.name, "B": w.B, "R": w.R if strong else w.R * world, "L": w.L, "H": w.H,
+                       "sigma": w.sigma, "seed": w.seed,
+                       "sharding": (f"by head, no collective: {shard.h1 - shard.h0} of {w.R if strong else w.R * world} "
+                                    f"heads x {shard.b1 - shard.b0} batch entries per GPU"),
                        "kernel": kernel,
                        "l2": f"{nbuf} rotating copies of the inputs, {nbuf * shard_bytes / 2**20:.0f} MiB working "
                              f"set > 126 MiB L2"},
@@ -318,7 +325,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default=None)
-    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="weak")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement (profiling runs)")
     args = ap.parse_args()

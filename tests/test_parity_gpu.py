@@ -99,6 +99,17 @@ def test_many_batches_and_heads_index_correctly():
         assert_close(run(q, k, v, 64, flags=flags), expected)
 
 
+@pytest.mark.parametrize("B,R,L,H", [(40, 8, 100, 64), (40, 8, 200, 64), (20, 10, 300, 128), (3, 100, 130, 64),
+                                     (2, 160, 257, 128)])
+def test_persistent_kernel_with_several_items_per_cta(B, R, L, H):
+    """More work items than SMs with one, two or three key steps each: every CTA of the persistent
+    kernel walks several items, so the hand-overs between items (query buffers, O tiles, row sums)
+    are exercised at their tightest."""
+    q, k, v = make_inputs(B, L, R * H, 1.0, 2000 + L)
+    expected = oracle(q, k, v, H)
+    assert_close(run(q, k, v, H, flags=PIPE), expected)
+
+
 def test_large_logits_stay_finite():
     # sigma 4 at H=128 gives scores of a few hundred before scaling: exercises the running max
     q, k, v = make_inputs(1, 512, 256, 4.0, 5)
