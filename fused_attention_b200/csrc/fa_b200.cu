@@ -131,11 +131,13 @@ int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask,
     if (flags & FA_B200_FLAG_FORCE_SIMPLE) return 1;
     if (flags & FA_B200_FLAG_FORCE_PIPELINED) return 2;
     if (has_mask || H < 64) return 1;
-    // The pipelined kernel works on pairs of query tiles and wants one CTA per SM to have a
-    // long key loop; short sequences or too few CTAs to fill the SMs go to the simple kernel.
+    // The pipelined kernel works on items of two query tiles (256 rows) on persistent CTAs.  It wins
+    // as soon as there are enough items to occupy a good part of the SMs (measured: 39 vs 57 us on
+    // B=64 R=16 L=197 H=64); a single partial tile or a handful of items goes to the simple kernel,
+    // which has twice as many, smaller CTAs.
     const uint64_t pairs = static_cast<uint64_t>((L + 255) / 256) * (F / H) * B;
-    if (L <= 256) return 1;
-    if (pairs < static_cast<uint64_t>(sm_count)) return 1;
+    if (L <= 128) return 1;
+    if (pairs * 2 < static_cast<uint64_t>(sm_count)) return 1;
     return 2;
 }
 
