@@ -3,7 +3,9 @@
   libfa_b200.so   CUDA kernels + C ABI (torch-free), nvcc, sm_100a only
   fused_attn*.so  the torch extension module ``fused_attn`` (thin C++ binding over the C ABI)
 
-Run ``python -m fused_attention_b200.build [--ext]``.  Nothing is installed outside the tree.
+  bin/fa_b200_driver  torch-free C++ program over the C ABI (fill, run, check, time)
+
+Run ``python -m fused_attention_b200.build [--ext] [--driver]``.  Nothing is installed outside the tree.
 """
 from __future__ import annotations
 
@@ -90,11 +92,31 @@ def build_ext(force: bool = False) -> str:
     return out
 
 
+def driver_path() -> str:
+    return os.path.join(HERE, "bin", "fa_b200_driver")
+
+
+def build_driver(force: bool = False) -> str:
+    """Compile csrc/fa_driver.cu, the torch-free program over the C ABI, into bin/fa_b200_driver."""
+    build_lib()
+    src = os.path.join(CSRC, "fa_driver.cu")
+    out = driver_path()
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    if not force and not _stale(out, [src, LIB]):
+        return out
+    cmd = [_nvcc(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"),
+           "-o", out, src, f"-L{LIBDIR}", "-lfa_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 def main(argv: list[str]) -> int:
     force = "--force" in argv
     print(build_lib(force=force, verbose="-v" in argv))
     if "--ext" in argv:
         print(build_ext(force=force))
+    if "--driver" in argv:
+        print(build_driver(force=force))
     return 0
 
 

@@ -312,3 +312,18 @@ def test_closer_to_the_oracle_than_the_reference_fused_kernel(H, C, B, R, L):
     err_ref = error_metrics(_run_ref_wmma(lib, q, k, v, H, C).float().cpu(), expected)
     err_new = assert_close(fa.attention_forward(H, C, q, k, v).float().cpu(), expected)
     assert err_new["max_abs"] <= err_ref["max_abs"] and err_new["mean_abs"] <= err_ref["mean_abs"], (err_new, err_ref)
+
+
+# ---------------------------------------------------------------- torch-free C++ driver
+@pytest.mark.parametrize("shape", [(2, 4, 600, 128), (3, 2, 197, 64), (1, 2, 100, 32)])
+def test_torch_free_driver_program(shape):
+    """The C++ program over the C ABI (the role of the reference's src/test.cu): fills with an LCG,
+    runs both entry points, checks sampled rows against a plain CPU loop and exits non-zero on a miss."""
+    import subprocess
+    from fused_attention_b200 import build
+    exe = build.driver_path()
+    if not os.path.exists(exe):
+        pytest.skip("driver not built (python -m fused_attention_b200.build --driver)")
+    r = subprocess.run([exe, *map(str, shape), "5"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "differ in 0 values" in r.stdout
