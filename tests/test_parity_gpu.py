@@ -121,6 +121,30 @@ def test_large_logits_stay_finite():
         assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m   # |V| reaches 16 here
 
 
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("pattern", ["rising", "falling", "spike"])
+def test_reference_maximum_moves_between_key_tiles(H, pattern):
+    """Scores that jump by far more than 2^8 (in the exp2 domain) from one key tile to the next:
+    rising (every tile forces a new reference and an O rescale), falling (the first reference stays,
+    later P underflow to zero) and a single late spike."""
+    B, R, L = 2, 3, 128 * 6 + 50
+    q, k, v = make_inputs(B, L, R * H, 1.0, 4000 + H)
+    q = (q.float() * 0.05 + 1.0).half()                      # close to all-ones queries
+    tile = torch.arange(L) // 128
+    if pattern == "rising":
+        level = 70.0 * tile
+    elif pattern == "falling":
+        level = 70.0 * (tile.max() - tile)
+    else:
+        level = torch.zeros(L); level[128 * 4 + 17] = 300.0
+    k = (k.float() * 0.05 + (level / H)[None, :, None]).half()   # raw score of key j is about level[j]
+    expected = oracle(q, k, v, H)
+    for flags in (SIMPLE, PIPE):
+        y = run(q, k, v, H, flags=flags)
+        assert torch.isfinite(y).all()
+        assert_close(y, expected)
+
+
 def test_kernels_agree_and_are_deterministic():
     q, k, v = make_inputs(2, 700, 256, 1.0, 11)
     a = run(q, k, v, 128, flags=PIPE)
