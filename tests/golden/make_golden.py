@@ -1,7 +1,7 @@
 """Generate tests/golden/*.npz from the REFERENCE's own naive attention.
 
 Needs the reference checkout (read-only) to import tests/naive_implementation.py::attention; run
-once in the authoring container:   python tests/golden/make_golden.py /root/reference
+once where the reference checkout is available:   python tests/golden/make_golden.py <reference checkout>
 Each file holds fp16 inputs q, k, v [B, L, F], the head_dim, and y = reference attention of the
 inputs upcast to fp32, on the CPU.
 """
