@@ -84,12 +84,13 @@ int ensure_ctx(int device, DeviceCtx** out) {
 }
 
 // 3-D map {F, L, B} over a contiguous [B, L, F] fp16 array; box = 128 rows x min(H, 64) columns.
-int make_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L, uint32_t F, uint32_t H) {
+int make_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L, uint32_t F, uint32_t H,
+             uint32_t box_rows = static_cast<uint32_t>(fa::kTile)) {
     const uint32_t box_cols = H < 64 ? H : 64;
     const cuuint64_t dims[3] = {F, L, B};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(F) * 2ull,
                                    static_cast<cuuint64_t>(F) * 2ull * L};
-    const cuuint32_t box[3] = {box_cols, static_cast<cuuint32_t>(fa::kTile), 1};
+    const cuuint32_t box[3] = {box_cols, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapSwizzle swz = box_cols == 64   ? CU_TENSOR_MAP_SWIZZLE_128B
                                    : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
@@ -158,7 +159,7 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
 
 template <int H>
 int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
-                     const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, cudaStream_t st) {
     constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
     auto kern = fa::fa_fwd_pipelined<H>;
     if (!(c.attr_done & (1u << slot))) {
@@ -168,7 +169,7 @@ int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtens
     }
     const uint32_t sms = static_cast<uint32_t>(c.sm_count);
     const dim3 grid(p.n_items < sms ? p.n_items : sms, 1, 1);   // persistent: one CTA per SM
-    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+    kern<<<grid, 512, smem, st>>>(mq, mk, mv, my, p);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -213,8 +214,12 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
 #endif
                 const int which = select_kernel(B, L, F, H, mask != nullptr, flags, c->sm_count);
                 if (which == 2) {
-                    rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, p, st)
-                                  : launch_pipelined<64>(*c, 9, mq, mk, mv, p, st);
+                    // Y as a TMA store target: boxes of 32 rows x 64 columns (one epilogue warp each)
+                    CUtensorMap my;
+                    rc = make_map(&my, y, B, L, F, H, 32);
+                    if (rc == FA_B200_OK)
+                        rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, my, p, st)
+                                      : launch_pipelined<64>(*c, 9, mq, mk, mv, my, p, st);
                 } else if (mask) {
                     switch (H) {
                         case 16: rc = launch_simple<16, true>(*c, 4, mq, mk, mv, p, st); break;

@@ -414,7 +414,8 @@ struct PipeCfg {
     static constexpr int kStages = H == 128 ? 4 : 8;   // ring slots of one K or V tile each
     static constexpr int kQBytes = 2 * G::kTileBytes;  // two query tiles
     static constexpr int kRingBytes = kStages * G::kTileBytes;
-    static constexpr int kSmemBytes = kQBytes + kRingBytes + 1024;  // + alignment slack
+    static constexpr int kStageBytes = 4 * 32 * 128;   // epilogue staging: per warp 32 rows x 64 fp16
+    static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
     // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+H) O1 [384,384+H)
     static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
@@ -439,7 +440,8 @@ struct PipeCfg {
 template <int H>
 __global__ void __launch_bounds__(512, 1)
 fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const Params p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmY,
+                 const Params p) {
     using G = TileGeom<H>;
     using C = PipeCfg<H>;
     constexpr int NS = C::kStages;
@@ -474,11 +476,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;                   // two tiles
     const uint32_t sRing = smem_base + C::kQBytes;   // NS tiles
+    const uint32_t sStage = sRing + C::kRingBytes;   // epilogue staging, 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
     const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles};
 
     if (tid == 0) {
+        prefetch_tensormap(&tmY);
 #pragma unroll
         for (int i = 0; i < BAR_COUNT; ++i) {
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
@@ -569,9 +573,15 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ epilogue: Y = O / l
+        // Each warp owns 32 rows of the tile.  It reads them from TMEM 64 columns at a time, scales
+        // by 1/l, rounds to fp16 and writes 16-byte vectors into its 4 KiB staging buffer (rows of
+        // 128 bytes, 128-byte swizzle), which one TMA store sends to Y: the warp is not held up by
+        // scattered global stores and the O tile is handed back as soon as it is in registers.
         setmaxnreg_dec<64>();
         const uint32_t row = tid & 127u;
-        const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
+        const uint32_t wq = warp & 3u;
+        const uint32_t lane_off = (wq * 32u) << 16;
+        const uint32_t stage = sStage + wq * 4096u;
         uint32_t k = 0;
         for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
             const uint32_t q_pair = item % q_pairs, bh = item / q_pairs;
@@ -580,22 +590,55 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (uint32_t i = 0; i < 2; ++i) {
                 // this wait lasts for a whole item: poll every 100 ns
                 mbar_wait_relaxed(bar(BAR_A0 + i), k & 1u, ctl, kRoleCorrection | (BAR_A0 + i), 100);
-                const float l = l_buf[k & 1u][i][row];
+                const float inv_l = 1.f / l_buf[k & 1u][i][row];
                 // The item's last P V of this tile.  Every earlier phase of this barrier has
                 // completed by the time the softmax warps signalled and the next phase needs this
                 // epilogue's OFREE arrival, so the parity test is unambiguous.
                 mbar_wait(bar(BAR_PV0 + i), (k * n + n - 1u) & 1u, ctl, kRoleCorrection | (BAR_PV0 + i));
                 tc_fence_after();
                 __syncwarp();
-                const uint32_t q_row = (q_pair * 2u + i) * kTile + row;
-                __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
-                store_o_row<H>(tmem_base + lane_off + (i ? C::kColO1 : C::kColO0), 1.f / l, dst,
-                               q_row < p.L);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+                const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
+                const int32_t row0 = static_cast<int32_t>((q_pair * 2u + i) * kTile + wq * 32u);
+#pragma unroll
+                for (int half = 0; half < H / 64; ++half) {
+                    // the previous store out of this staging buffer must have read it completely
+                    if (lane == 0) bulk_wait_read_all();
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {   // 16 columns at a time keeps this role within 64 registers
+                        float o[16];
+                        tmem_ld16(tO + half * 64 + c * 16, o);
+                        tmem_wait_ld();
+                        if (half == H / 64 - 1 && c == 3) {
+                            // the whole O tile has left TMEM: the MMA warp may overwrite it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+                        }
+#pragma unroll
+                        for (int v4 = 0; v4 < 2; ++v4) {
+                            const uint32_t w0 = pack_half2(o[v4 * 8 + 0] * inv_l, o[v4 * 8 + 1] * inv_l);
+                            const uint32_t w1 = pack_half2(o[v4 * 8 + 2] * inv_l, o[v4 * 8 + 3] * inv_l);
+                            const uint32_t w2 = pack_half2(o[v4 * 8 + 4] * inv_l, o[v4 * 8 + 5] * inv_l);
+                            const uint32_t w3 = pack_half2(o[v4 * 8 + 6] * inv_l, o[v4 * 8 + 7] * inv_l);
+                            // logical 16-byte chunk c*2+v4 of row `lane`, 128-byte swizzle
+                            const uint32_t chunk = static_cast<uint32_t>(c * 2 + v4) ^ (lane & 7u);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128u + chunk * 16u),
+                                         "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                                         : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < static_cast<int32_t>(p.L)) {   // rows past L are clipped by the store
+                        tma_store_3d(&tmY, stage, static_cast<int32_t>(head * H + half * 64), row0,
+                                     static_cast<int32_t>(batch));
+                        bulk_commit_group();
+                    }
+                }
             }
         }
+        if (lane == 0) bulk_wait_all();   // Y is complete before the CTA leaves
     } else {
         setmaxnreg_dec<80>();
         if (warp == 12) {
