@@ -12,6 +12,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "fa_b200.h"
@@ -28,9 +29,10 @@ struct DeviceCtx {
     bool ready = false;
     int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
     uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count}
-    uint32_t attr_done = 0;       // bit per kernel instance whose smem attribute is set
+    std::atomic<uint32_t> attr_done{0};   // bit per kernel instance whose smem attribute is set
     // host-buffer entry point: copy-in / compute / copy-out streams, per-chunk events and
     // grow-on-demand staging buffers
+    std::mutex host_mu;   // one host-buffer call at a time per device: they share the staging buffers
     cudaStream_t host_stream = nullptr, host_stream2 = nullptr, host_stream3 = nullptr;
     cudaEvent_t ev_in[8] = {}, ev_cmp[8] = {};
     void* stage[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v y mask
@@ -147,10 +149,10 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
                   const CUtensorMap& mv, const Params& p, cudaStream_t st) {
     constexpr int smem = 3 * fa::TileGeom<H>::kTileBytes + 1024;
     auto kern = fa::fa_fwd_simple<H, M>;
-    if (!(c.attr_done & (1u << slot))) {
+    if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
-        c.attr_done |= (1u << slot);
+        c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
     const dim3 grid((p.L + fa::kTile - 1) / fa::kTile, p.F / H, p.B);
     kern<<<grid, 128, smem, st>>>(mq, mk, mv, p);
@@ -162,10 +164,10 @@ int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtens
                      const CUtensorMap& mv, const CUtensorMap& my, const Params& p, cudaStream_t st) {
     constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
     auto kern = fa::fa_fwd_pipelined<H>;
-    if (!(c.attr_done & (1u << slot))) {
+    if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
-        c.attr_done |= (1u << slot);
+        c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
     const uint32_t sms = static_cast<uint32_t>(c.sm_count);
     const dim3 grid(p.n_items < sms ? p.n_items : sms, 1, 1);   // persistent: one CTA per SM
@@ -186,8 +188,10 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
     int rc = FA_B200_OK;
     DeviceCtx* c = nullptr;
     {
-        std::lock_guard<std::mutex> lk(g_mu);
+        std::lock_guard<std::mutex> lk(g_mu);   // only the once-per-device set-up is serialised
         rc = ensure_ctx(device, &c);
+    }
+    {
         if (rc == FA_B200_OK && c->cc_major != 10) rc = FA_B200_ERR_ARCH;
         if (rc == FA_B200_OK) {
             CUtensorMap mq, mk, mv;
@@ -448,6 +452,12 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
             }
             if (e != cudaSuccess) rc = static_cast<int>(e);
         }
+    }
+    std::unique_lock<std::mutex> host_lock;
+    if (rc == FA_B200_OK) host_lock = std::unique_lock<std::mutex>(c->host_mu);
+    if (rc == FA_B200_OK) {
+        // the staging buffers are sized under the device's host lock, so a concurrent call cannot
+        // free them while this one is using them
         for (int i = 0; i < 4 && rc == FA_B200_OK; ++i) rc = grow(*c, i, bytes);
         if (rc == FA_B200_OK && mbytes) rc = grow(*c, 4, mbytes);
     }

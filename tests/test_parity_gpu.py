@@ -217,6 +217,45 @@ def test_host_buffer_entry_point_matches_device_entry_point():
     assert torch.equal(run(q2, k2, v2, 32), fa.attention_forward_host(32, 32, q2, k2, v2).float())
 
 
+def test_concurrent_callers_from_several_threads():
+    """The C ABI is thread-safe: device-pointer calls on separate streams and host-buffer calls
+    (which share per-device staging buffers and must serialise themselves) from four threads."""
+    import threading
+    q, k, v = make_inputs(2, 700, 256, 1.0, 91)
+    expected = run(q, k, v, 128)
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    results, errors = {}, []
+
+    def device_worker(idx):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(10):
+                    y = fa.attention_forward(128, 64, dq, dk, dv)
+            s.synchronize()
+            results[idx] = y.float().cpu()
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    def host_worker(idx):
+        try:
+            for _ in range(3):
+                y = fa.attention_forward_host(128, 64, q, k, v)
+            results[idx] = y.float()
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=device_worker, args=(0,)), threading.Thread(target=device_worker, args=(1,)),
+               threading.Thread(target=host_worker, args=(2,)), threading.Thread(target=host_worker, args=(3,))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for idx in range(4):
+        assert torch.equal(results[idx], expected)
+
+
 def test_non_default_stream_and_output_placement():
     q, k, v = (t.cuda() for t in make_inputs(1, 512, 256, 1.0, 31))
     s = torch.cuda.Stream()
