@@ -91,6 +91,31 @@ def test_ragged_lengths(H, L):
         assert_close(run(q, k, v, H, flags=flags), expected)
 
 
+def _fuzz_cases():
+    import random
+    rng = random.Random(20261125)
+    cases = []
+    for _ in range(24):
+        H = rng.choice([16, 32, 64, 64, 128, 128])
+        B = rng.randint(1, 5)
+        R = rng.randint(1, 9)
+        L = rng.choice([rng.randint(1, 130), rng.randint(131, 700), rng.randint(701, 1500)])
+        flags = rng.choice([0, SIMPLE] + ([PIPE, PIPE] if H >= 64 else []))
+        sigma = rng.choice([0.5, 1.0, 2.0])
+        cases.append((H, B, R, L, flags, sigma))
+    return cases
+
+
+@pytest.mark.parametrize("H,B,R,L,flags,sigma", _fuzz_cases())
+def test_seeded_random_shapes(H, B, R, L, flags, sigma):
+    q, k, v = make_inputs(B, L, R * H, sigma, 7000 + L + H)
+    expected = oracle(q, k, v, H)
+    y = run(q, k, v, H, flags=flags)
+    m = error_metrics(y, expected)
+    scale = max(1.0, sigma)          # |V| grows with sigma; the bound is for unit-scale values
+    assert m["max_abs"] <= MAX_ABS_TOL * scale and m["mean_abs"] <= MEAN_ABS_TOL * scale, m
+
+
 def test_many_batches_and_heads_index_correctly():
     # every (batch, head) pair gets its own inputs; a wrong offset shows as a large error
     q, k, v = make_inputs(5, 200, 7 * 64, 1.0, 77)
