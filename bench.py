@@ -288,6 +288,8 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
                        "l2": f"{nbuf} rotating copies of the inputs, {nbuf * shard_bytes / 2**20:.0f} MiB working "
                              f"set > 126 MiB L2"},
             "pct_of_peak": {"measured_dense_bf16_burst": 100.0 * value / (peak * world),
+                            "measured_dense_bf16_sustained": (100.0 * value / (float(peaks["bf16_tflops_sustained"]) * world)
+                                                              if "bf16_tflops_sustained" in peaks else None),
                             "nominal_dense_fp16_2250": 100.0 * value / (2250.0 * world), "peak_source": peak_kind},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
