@@ -557,7 +557,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         l += sum;
                     }
                 }
+                if (tr_me) FA_TRACE_EV(1 + i, 5);   // exponentials issued
                 tmem_wait_st();
+                if (tr_me) FA_TRACE_EV(1 + i, 6);   // P stores retired
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));

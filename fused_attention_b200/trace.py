@@ -1,0 +1,115 @@
+"""Per-role time line of one CTA of the pipelined kernel.
+
+    python -m fused_attention_b200.trace [--workload NAME] [--cta N]
+
+Builds ``lib/libfa_b200_trace.so`` from the same sources with ``-DFA_TRACE`` (the normal library has
+no tracing code), runs the workload once with one CTA recording ``clock64`` at its hand-over points,
+and prints, in SM clocks: the length of a key step, how long the MMA warp spends issuing each group of
+MMAs and waiting for each P, and how long a softmax warp spends on each part of its step.  This is a
+diagnostic for kernel work; it is not used by the operator, the tests or the benchmark.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import os
+import subprocess
+import sys
+
+from . import build as _build
+
+TRACE_LIB = os.path.join(_build.LIBDIR, "libfa_b200_trace.so")
+MMA_TAGS = {1: "V and next K landed", 2: "P0 ready", 8: "PV0 issued", 4: "QK0 issued", 5: "P1 ready",
+            10: "PV1 issued", 7: "QK1 issued"}
+SM_TAGS = {1: "S ready", 2: "S in registers", 5: "exponentials issued", 6: "P stores retired", 4: "P signalled"}
+
+
+def build_trace_lib(force: bool = False) -> str:
+    srcs = _build.lib_sources()
+    if not force and os.path.exists(TRACE_LIB) and all(os.path.getmtime(s) < os.path.getmtime(TRACE_LIB) for s in srcs):
+        return TRACE_LIB
+    os.makedirs(_build.LIBDIR, exist_ok=True)
+    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DFA_TRACE", "-I", os.path.join(_build.ROOT, "include"), "-I", _build.CSRC,
+           "-o", TRACE_LIB, os.path.join(_build.CSRC, "fa_b200.cu")]
+    subprocess.run(cmd, check=True)
+    return TRACE_LIB
+
+
+def _mean(xs):
+    xs = list(xs)
+    return sum(xs) / len(xs) if xs else float("nan")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--cta", type=int, default=20, help="which CTA records (block index)")
+    args = ap.parse_args(argv)
+
+    import torch
+    from .workloads import HEADLINE, WORKLOADS, workload_inputs
+
+    w = WORKLOADS[args.workload or HEADLINE]
+    lib = ctypes.CDLL(build_trace_lib())
+    u32, vp, i32 = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
+    lib.fa_b200_attention_forward.restype = i32
+    lib.fa_b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
+    lib.fa_b200_trace_setup.argtypes = [vp, u32]
+    q, k, v = (t.cuda() for t in workload_inputs(w))
+    y = torch.empty_like(q)
+    buf = torch.zeros(8 * 512, dtype=torch.int64, device="cuda")
+
+    def run():
+        rc = lib.fa_b200_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, y.data_ptr(),
+                                           w.B, w.L, w.F, w.H, 0, 0, None, 2)   # 2 = pipelined kernel
+        if rc != 0:
+            raise RuntimeError(f"status {rc}")
+
+    lib.fa_b200_trace_setup(None, 0)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    lib.fa_b200_trace_setup(buf.data_ptr(), args.cta)
+    run()
+    torch.cuda.synchronize()
+    lib.fa_b200_trace_setup(None, 0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    print(f"workload {w.name}: {ms * 1e3:.1f} us per launch, {w.flops / ms / 1e9:.1f} TFLOP/s (trace build)")
+
+    t = buf.cpu().view(8, 512)
+    slots = {0: "mma", 1: "softmax0", 2: "softmax1"}
+    ev = {name: [(x >> 8, x & 255) for x in t[s].tolist() if x] for s, name in slots.items()}
+    n = max(1, (w.L + 127) // 128)
+    mma = ev["mma"]
+    ends = [c for c, g in mma if g == 7]
+    periods = [b - a for a, b in zip(ends, ends[1:])]
+    steady = sorted(periods)[: max(1, len(periods) * 3 // 4)]          # drop the item-boundary steps
+    print(f"key steps per item: {n}; clocks per key step: median of the steady ones {steady[len(steady) // 2]}, "
+          f"all {periods[:24]}")
+    seg = {}
+    for (c0, g0), (c1, g1) in zip(mma, mma[1:]):
+        seg.setdefault((g0, g1), []).append(c1 - c0)
+    print("MMA warp, mean clocks from one point to the next:")
+    for (g0, g1), vals in seg.items():
+        if len(vals) >= 4:
+            print(f"  {MMA_TAGS.get(g0, g0):>22} -> {MMA_TAGS.get(g1, g1):<22} {_mean(vals):7.0f}")
+    for name in ("softmax0", "softmax1"):
+        e = ev[name]
+        seg = {}
+        for (c0, g0), (c1, g1) in zip(e, e[1:]):
+            seg.setdefault((g0, g1), []).append(c1 - c0)
+        print(f"{name} (row 0's thread), mean clocks:")
+        for (g0, g1), vals in seg.items():
+            if len(vals) >= 4:
+                print(f"  {SM_TAGS.get(g0, g0):>22} -> {SM_TAGS.get(g1, g1):<22} {_mean(vals):7.0f}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
