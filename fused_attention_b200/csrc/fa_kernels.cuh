@@ -114,13 +114,15 @@ __device__ __forceinline__ void issue_qk(uint32_t tS, uint32_t sQ, uint32_t sK) 
 }
 
 // O[128 x H] (+)= P[128 x 128] * V[128 x H]; P is fp16 in TMEM, V is MN-major in shared memory.
-template <int H>
+// Issues the k-steps [kK0, kK1) of the eight (16 keys each), so that the product can start on the
+// part of P that is already written.
+template <int H, int kK0 = 0, int kK1 = kTile / 16>
 __device__ __forceinline__ void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, uint32_t accumulate) {
     using G = TileGeom<H>;
     constexpr uint32_t idesc = make_idesc_f16(H, 1);
     const uint64_t dv = make_smem_desc<G::kSwz>(sV, G::kBoxBytes);
 #pragma unroll
-    for (int ks = 0; ks < kTile / 16; ++ks) {
+    for (int ks = kK0; ks < kK1; ++ks) {
         // 16 key rows per step: 8 TMEM columns of packed fp16 pairs, 16 shared-memory rows.
         mma_ts(tO, tP + ks * 8, dv + ((ks * 16 * G::kSwz) >> 4), idesc, (accumulate | ks) ? 1u : 0u);
     }
@@ -208,6 +210,58 @@ __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const 
         tmem_st16(tP + chunk * 16, pk);
     }
     if (kWithMax) mx_out = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+    float lo, hi;
+    unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
+    return lo + hi;
+}
+
+// Knobs of the pipelined kernel's softmax (compile-time; the defaults are the measured best).
+//   FA_SPLIT_P     how many 32-key chunks of P a softmax warp hands to the MMA warp first; the
+//                  rest follows with a second arrival, so that P V starts while the last
+//                  exponentials are still being taken (4 = the whole row at once)
+//   FA_POLY_PAIRS  of every 16 pairs of exponentials, how many are computed on the FMA pipe
+//   FA_LD_PIPE     1 = the first 32 scores are waited for alone and worked on while the other 96
+//                  are still on their way from TMEM
+#ifndef FA_SPLIT_P
+#define FA_SPLIT_P 3
+#endif
+#ifndef FA_POLY_PAIRS
+#define FA_POLY_PAIRS 0
+#endif
+#ifndef FA_LD_PIPE
+#define FA_LD_PIPE 0
+#endif
+
+// P = exp2(s*c + nmc) for the 32-key chunks [kC0, kC1) of one score row, written as fp16 into TMEM
+// at tP + 16*chunk (two values per column, even key index in the low half); returns the fp32 sum of
+// those P.  With kWithMax the running maxima mx[] take in the scores of these chunks in the same
+// pass (the maximum instructions fill the issue slots the MUFU leaves free).
+template <int kC0, int kC1, bool kWithMax>
+__device__ __forceinline__ float exp_chunks(const float (&s)[kTile], const float c, const float nmc,
+                                            const uint32_t tP, float (&mx)[4]) {
+    const uint64_t c2 = pack_f32x2(c, c), n2 = pack_f32x2(nmc, nmc);
+    uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+    for (int chunk = kC0; chunk < kC1; ++chunk) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float s0 = s[chunk * 32 + 2 * e], s1 = s[chunk * 32 + 2 * e + 1];
+            float x0, x1, p0, p1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2, n2), x0, x1);
+            if (FA_POLY_PAIRS > 0 && ((e * FA_POLY_PAIRS) % 16) < FA_POLY_PAIRS) {
+                ex2_poly_x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f), p0, p1);
+            } else {
+                p0 = ex2_approx(x0);
+                p1 = ex2_approx(x1);
+            }
+            if (e & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
+            else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+            pk[e] = pack_half2(p0, p1);
+            if (kWithMax) mx[e & 3] = max3(mx[e & 3], s0, s1);
+        }
+        tmem_st16(tP + chunk * 16, pk);
+    }
     float lo, hi;
     unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
     return lo + hi;
@@ -451,6 +505,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
         BAR_P0, BAR_P1,              // softmax -> MMA: P written (and O rescaled in the rare steps
                                      // that need it); 4 arrivals, one per softmax warp
+        BAR_PB0, BAR_PB1,            // softmax -> MMA: part b of P written (4 arrivals)
+        BAR_PVA0, BAR_PVA1,          // MMA -> softmax: P V of part a complete (waited for only in the
+                                     // rare steps whose reference moves within part b)
         BAR_PV0, BAR_PV1,            // MMA -> softmax (rescale steps) and epilogue: P V complete
         BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
         BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
@@ -487,7 +544,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < BAR_COUNT; ++i) {
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
-            const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_A0 || i == BAR_A1 ||
+            const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_PB0 || i == BAR_PB1 ||
+                                   i == BAR_A0 || i == BAR_A1 ||
                                    i == BAR_OFREE0 || i == BAR_OFREE1);
             mbar_init(bar(i), per_warp ? 4u : 1u);
         }
@@ -527,28 +585,50 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 __syncwarp();
                 if (tr_me) FA_TRACE_EV(1 + i, 1);   // S ready
                 float s[kTile];
+                const bool ragged = (j + 1) * kTile > p.L;
+                const bool first = j == 0;
+#if FA_LD_PIPE
+                tmem_ld32(tS, s);
+                tmem_wait_ld_tied(s);
+                tmem_ld32(tS + 32, s + 32);
+                tmem_ld32(tS + 64, s + 64);
+                tmem_ld32(tS + 96, s + 96);
+                if (ragged || first) {   // both need the whole row before the first exponential
+                    tmem_wait_ld_tied(s + 32);
+                    tmem_wait_ld_tied(s + 64);
+                    tmem_wait_ld_tied(s + 96);
+                    if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
+                    if (first) m = row_max(s);   // first key tile: the reference is its row maximum
+                }
+#else
                 load_s_row(tS, s);
-                if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
-                if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
-                float unused;
-                if (j == 0) {
-                    // first key tile: the reference maximum is this tile's row maximum
-                    m = row_max(s);
-                    l = exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
-                } else {
-                    // Later tiles: take the exponentials against the current reference while the
-                    // row maximum is computed in the same pass.  The reference only has to move
-                    // when the new maximum exceeds it by more than 2^8 in the exp2 domain.
-                    float mx;
-                    const float sum = exp_and_store_p<true, true>(s, c, -m * c, tS, mx);
+                if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
+                if (first) m = row_max(s);
+#endif
+                if (tr_me) FA_TRACE_EV(1 + i, 2);   // first scores in registers
+                // Part a, chunks [0, FA_SPLIT_P): exponentials against the standing reference, with
+                // the maximum of these scores taken in the same pass.  The reference only has to
+                // move when a score exceeds it by more than 2^8 in the exp2 domain.
+                {
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    float sum = exp_chunks<0, 1, true>(s, c, -m * c, tS, mx4);
+#if FA_LD_PIPE
+                    tmem_wait_ld_tied(s + 32);
+                    tmem_wait_ld_tied(s + 64);
+                    tmem_wait_ld_tied(s + 96);
+#endif
+                    sum += exp_chunks<1, FA_SPLIT_P, true>(s, c, -m * c, tS, mx4);
+                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
                         // Some row of this warp needs a new reference: redo the warp's exponentials
-                        // (rows that keep theirs reproduce the same P) and rescale O by alpha.
+                        // (rows that keep theirs reproduce the same P) and rescale O by alpha once
+                        // the previous step's P V has retired.
                         const float m_new = moved ? mx : m;
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
-                        l = l * alpha + exp_and_store_p<false, true>(s, c, -m * c, tS, unused);
+                        float unused[4];
+                        l = l * alpha + exp_chunks<0, FA_SPLIT_P, false>(s, c, -m * c, tS, unused);
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -557,13 +637,41 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         l += sum;
                     }
                 }
-                if (tr_me) FA_TRACE_EV(1 + i, 5);   // exponentials issued
+                if (tr_me) FA_TRACE_EV(1 + i, 5);   // part a's exponentials issued
                 tmem_wait_st();
-                if (tr_me) FA_TRACE_EV(1 + i, 6);   // P stores retired
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
-                if (tr_me) FA_TRACE_EV(1 + i, 4);   // P written
+                if (tr_me) FA_TRACE_EV(1 + i, 4);   // part a of P signalled
+#if FA_SPLIT_P < 4
+                // Part b, the remaining chunks, while the MMA warp already multiplies part a by V.
+                {
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    const float sum = exp_chunks<FA_SPLIT_P, 4, true>(s, c, -m * c, tS, mx4);
+                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                    const bool moved = (mx - m) * c > kLazyRescaleLog2;
+                    if (__any_sync(0xffffffffu, moved)) {
+                        // The new reference shows up in part b only: O (which by now takes in part a
+                        // against the old reference) is rescaled once part a's P V has retired.
+                        const float m_new = moved ? mx : m;
+                        const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
+                        m = m_new;
+                        float unused[4];
+                        l = l * alpha + exp_chunks<FA_SPLIT_P, 4, false>(s, c, -m * c, tS, unused);
+                        mbar_wait(bar(BAR_PVA0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_PVA0 + i));
+                        tc_fence_after();
+                        __syncwarp();
+                        rescale_o_row<H>(tO, alpha);
+                    } else {
+                        l += sum;
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(BAR_PB0 + i));
+                    if (tr_me) FA_TRACE_EV(1 + i, 6);   // part b of P signalled
+                }
+#endif
             }
             // Hand the row sums to the epilogue.  The A barrier may run at most one phase ahead of
             // the epilogue's wait, so the previous item's O must have been read out first (always
@@ -699,10 +807,15 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
                 FA_TRACE_EV(0, 2);   // P0 ready
                 tc_fence_after();
-                if (leader) {
-                    issue_pv<H>(tO0, tS0, slot_addr(tv), acc);
-                    tc_commit(bar(BAR_PV0));
-                }
+                if (leader) issue_pv<H, 0, 2 * FA_SPLIT_P>(tO0, tS0, slot_addr(tv), acc);
+#if FA_SPLIT_P < 4
+                if (leader) tc_commit(bar(BAR_PVA0));
+                mbar_wait(bar(BAR_PB0), g & 1u, ctl, kRoleMma | BAR_PB0);
+                FA_TRACE_EV(0, 3);   // part b of P0 ready
+                tc_fence_after();
+                if (leader) issue_pv<H, 2 * FA_SPLIT_P, 8>(tO0, tS0, slot_addr(tv), 1u);
+#endif
+                if (leader) tc_commit(bar(BAR_PV0));
                 FA_TRACE_EV(0, 8);   // P V of tile 0 issued
                 if (more && leader) {
                     issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
@@ -717,8 +830,15 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
                 FA_TRACE_EV(0, 5);   // P1 ready
                 tc_fence_after();
+                if (leader) issue_pv<H, 0, 2 * FA_SPLIT_P>(tO1, tS1, slot_addr(tv), acc);
+#if FA_SPLIT_P < 4
+                if (leader) tc_commit(bar(BAR_PVA1));
+                mbar_wait(bar(BAR_PB1), g & 1u, ctl, kRoleMma | BAR_PB1);
+                FA_TRACE_EV(0, 6);   // part b of P1 ready
+                tc_fence_after();
+                if (leader) issue_pv<H, 2 * FA_SPLIT_P, 8>(tO1, tS1, slot_addr(tv), 1u);
+#endif
                 if (leader) {
-                    issue_pv<H>(tO1, tS1, slot_addr(tv), acc);
                     tc_commit(bar(BAR_PV1));
                     free_slot(tv);
                 }

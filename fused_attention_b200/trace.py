@@ -19,9 +19,10 @@ import sys
 from . import build as _build
 
 TRACE_LIB = os.path.join(_build.LIBDIR, "libfa_b200_trace.so")
-MMA_TAGS = {1: "V and next K landed", 2: "P0 ready", 8: "PV0 issued", 4: "QK0 issued", 5: "P1 ready",
-            10: "PV1 issued", 7: "QK1 issued"}
-SM_TAGS = {1: "S ready", 2: "S in registers", 5: "exponentials issued", 6: "P stores retired", 4: "P signalled"}
+MMA_TAGS = {1: "V and next K landed", 2: "P0 part a ready", 3: "P0 part b ready", 8: "PV0 issued", 4: "QK0 issued",
+            5: "P1 part a ready", 6: "P1 part b ready", 10: "PV1 issued", 7: "QK1 issued"}
+SM_TAGS = {1: "S ready", 2: "S in registers", 5: "part a exponentials issued", 4: "part a signalled",
+           6: "part b signalled"}
 
 
 def build_trace_lib(force: bool = False) -> str:
@@ -29,7 +30,7 @@ def build_trace_lib(force: bool = False) -> str:
     if not force and os.path.exists(TRACE_LIB) and all(os.path.getmtime(s) < os.path.getmtime(TRACE_LIB) for s in srcs):
         return TRACE_LIB
     os.makedirs(_build.LIBDIR, exist_ok=True)
-    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DFA_TRACE", "-I", os.path.join(_build.ROOT, "include"), "-I", _build.CSRC,
+    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DFA_TRACE", *os.environ.get("FA_TRACE_FLAGS", "").split(), "-I", os.path.join(_build.ROOT, "include"), "-I", _build.CSRC,
            "-o", TRACE_LIB, os.path.join(_build.CSRC, "fa_b200.cu")]
     subprocess.run(cmd, check=True)
     return TRACE_LIB
@@ -44,6 +45,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--cta", type=int, default=20, help="which CTA records (block index)")
+    ap.add_argument("--dump", type=int, default=0, metavar="N",
+                    help="also print the merged time line of all roles over N key steps from the middle of the record")
     args = ap.parse_args(argv)
 
     import torch
@@ -108,6 +111,15 @@ def main(argv=None) -> int:
         for (g0, g1), vals in seg.items():
             if len(vals) >= 4:
                 print(f"  {SM_TAGS.get(g0, g0):>22} -> {SM_TAGS.get(g1, g1):<22} {_mean(vals):7.0f}")
+    if args.dump > 0 and len(ends) > args.dump + 4:
+        mid = len(ends) // 2
+        lo, hi = ends[mid], ends[mid + args.dump]
+        merged = sorted((c, name, g) for name, e in ev.items() for c, g in e if lo <= c <= hi)
+        print(f"merged time line of {args.dump} key steps (clocks from the first event):")
+        for c, name, g in merged:
+            tags = MMA_TAGS if name == "mma" else SM_TAGS
+            col = {"mma": 0, "softmax0": 1, "softmax1": 2}[name]
+            print(f"  {c - lo:7d}  " + " " * (30 * col) + f"{name}: {tags.get(g, g)}")
     return 0
 
 

@@ -147,11 +147,13 @@ def test_large_logits_stay_finite():
 
 
 @pytest.mark.parametrize("H", [64, 128])
-@pytest.mark.parametrize("pattern", ["rising", "falling", "spike"])
+@pytest.mark.parametrize("pattern", ["rising", "falling", "spike", "spike_in_last_keys_of_a_tile", "rising_by_32_keys"])
 def test_reference_maximum_moves_between_key_tiles(H, pattern):
     """Scores that jump by far more than 2^8 (in the exp2 domain) from one key tile to the next:
     rising (every tile forces a new reference and an O rescale), falling (the first reference stays,
-    later P underflow to zero) and a single late spike."""
+    later P underflow to zero) and a single late spike.  The pipelined kernel hands P of a key tile
+    to the MMA warp in two parts (keys 0-95, keys 96-127); the last two patterns put the new
+    maximum into the second part, after the first part has already been multiplied by V."""
     B, R, L = 2, 3, 128 * 6 + 50
     q, k, v = make_inputs(B, L, R * H, 1.0, 4000 + H)
     q = (q.float() * 0.05 + 1.0).half()                      # close to all-ones queries
@@ -160,8 +162,12 @@ def test_reference_maximum_moves_between_key_tiles(H, pattern):
         level = 70.0 * tile
     elif pattern == "falling":
         level = 70.0 * (tile.max() - tile)
-    else:
+    elif pattern == "spike":
         level = torch.zeros(L); level[128 * 4 + 17] = 300.0
+    elif pattern == "spike_in_last_keys_of_a_tile":
+        level = torch.zeros(L); level[128 * 3 + 101] = 300.0; level[128 * 5 + 127] = 450.0
+    else:
+        level = 70.0 * (torch.arange(L) // 32)
     k = (k.float() * 0.05 + (level / H)[None, :, None]).half()   # raw score of key j is about level[j]
     expected = oracle(q, k, v, H)
     for flags in (SIMPLE, PIPE):
