@@ -48,7 +48,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
-#ifdef FA_TRACE
+#if defined(FA_TRACE) || defined(FA_CYCLES)
 unsigned long long* g_trace_buf = nullptr;  // device buffer of 8 * 512 records, set by the trace hook
 uint32_t g_trace_cta = 0;
 #endif
@@ -212,7 +212,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.n_items = p.q_pairs * p.R * B;
                 p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
                 p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
-#ifdef FA_TRACE
+#if defined(FA_TRACE) || defined(FA_CYCLES)
                 p.trace = g_trace_buf;
                 p.trace_cta = g_trace_cta;
 #endif
@@ -373,7 +373,7 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
             p.n_items = p.q_pairs * p.R * B;
             p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
             p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
-#ifdef FA_TRACE
+#if defined(FA_TRACE) || defined(FA_CYCLES)
             p.trace = nullptr;
             p.trace_cta = 0;
 #endif
@@ -628,7 +628,7 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]) {
     return rc;
 }
 
-#ifdef FA_TRACE
+#if defined(FA_TRACE) || defined(FA_CYCLES)
 // Trace builds only: choose the recording CTA and the device buffer (8 * 512 * 8 bytes).
 int fa_b200_trace_setup(void* device_buffer, uint32_t cta) {
     g_trace_buf = static_cast<unsigned long long*>(device_buffer);

@@ -42,7 +42,7 @@ struct Params {
     uint32_t n_items;     // q_pairs * R * B: work items of the pipelined kernel
     float scale_log2;     // log2(e) / sqrt(H)
     float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
-#ifdef FA_TRACE
+#if defined(FA_TRACE) || defined(FA_CYCLES)
     unsigned long long* trace;  // [8 slots][512] (clock64 << 8 | tag) of one CTA, see FA_TRACE_EV
     uint32_t trace_cta;         // linear block index that records
 #endif
@@ -167,70 +167,35 @@ __device__ __forceinline__ float update_max(float& m, const float mx, const floa
     return alpha;
 }
 
-// Every FA_POLY_MOD-th pair of exponentials goes to the FMA-pipe polynomial instead of the MUFU
-// (0 = never).  The MUFU does 4 lanes per clock per sub-partition, so a 128-wide row costs a warp
-// about 1060 clocks there; moving a quarter of the pairs lets both pipes finish together.
-#ifndef FA_POLY_MOD
-#define FA_POLY_MOD 0
-#endif
-
-// P = exp2(s*c + nmc) for one score row: written as fp16 into 64 TMEM columns at tP (two values
-// per column, even key index in the low half); returns the fp32 row sum of P.  With kWithMax the
-// row maximum of s is computed in the same pass (its instructions fill the gaps the MUFU leaves).
-template <bool kWithMax, bool kPoly>
+// P = exp2(s*c + nmc) for one whole score row: written as fp16 into 64 TMEM columns at tP (two values
+// per column, even key index in the low half); returns the fp32 row sum of P.
 __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const float c,
-                                                 const float nmc, const uint32_t tP, float& mx_out) {
+                                                 const float nmc, const uint32_t tP) {
     const uint64_t c2 = pack_f32x2(c, c), n2 = pack_f32x2(nmc, nmc);
     uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const float s0 = s[chunk * 32 + 2 * e], s1 = s[chunk * 32 + 2 * e + 1];
-            float x0, x1, p0, p1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2, n2), x0, x1);
-            if (kPoly && FA_POLY_MOD > 0 && (e % (FA_POLY_MOD > 0 ? FA_POLY_MOD : 1)) == 1) {
-                ex2_poly_x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f), p0, p1);
-            } else {
-                p0 = ex2_approx(x0);
-                p1 = ex2_approx(x1);
-            }
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s[chunk * 32 + 2 * e], s[chunk * 32 + 2 * e + 1]), c2, n2), x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
             if (e & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
             else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
             pk[e] = pack_half2(p0, p1);
-            if (kWithMax) {
-                if ((e & 3) == 0) mx0 = max3(mx0, s0, s1);
-                else if ((e & 3) == 1) mx1 = max3(mx1, s0, s1);
-                else if ((e & 3) == 2) mx2 = max3(mx2, s0, s1);
-                else mx3 = max3(mx3, s0, s1);
-            }
         }
         tmem_st16(tP + chunk * 16, pk);
     }
-    if (kWithMax) mx_out = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     float lo, hi;
     unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
     return lo + hi;
 }
 
-// Knobs of the pipelined kernel's softmax (compile-time; the defaults are the measured best).
-//   FA_SPLIT_P     how many 32-key chunks of P a softmax warp hands to the MMA warp first; the
-//                  rest follows with a second arrival, so that P V starts while the last
-//                  exponentials are still being taken (4 = the whole row at once)
-//   FA_POLY_PAIRS  of every 16 pairs of exponentials, how many are computed on the FMA pipe
-//   FA_LD_PIPE     1 = the first 32 scores are waited for alone and worked on while the other 96
-//                  are still on their way from TMEM
-#ifndef FA_SPLIT_P
-#define FA_SPLIT_P 3
-#endif
-#ifndef FA_POLY_PAIRS
-#define FA_POLY_PAIRS 0
-#endif
-#ifndef FA_LD_PIPE
-#define FA_LD_PIPE 0
-#endif
+// The pipelined kernel's softmax hands P of a key tile to the MMA warp in two parts: the first
+// kSplitChunks chunks of 32 keys, then the rest with a second arrival, so that P V starts while the
+// last exponentials are still being taken.  Measured: 3 beats 2 and 4 (the whole row at once).
+constexpr int kSplitChunks = 3;
 
 // P = exp2(s*c + nmc) for the 32-key chunks [kC0, kC1) of one score row, written as fp16 into TMEM
 // at tP + 16*chunk (two values per column, even key index in the low half); returns the fp32 sum of
@@ -249,12 +214,8 @@ __device__ __forceinline__ float exp_chunks(const float (&s)[kTile], const float
             const float s0 = s[chunk * 32 + 2 * e], s1 = s[chunk * 32 + 2 * e + 1];
             float x0, x1, p0, p1;
             unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2, n2), x0, x1);
-            if (FA_POLY_PAIRS > 0 && ((e * FA_POLY_PAIRS) % 16) < FA_POLY_PAIRS) {
-                ex2_poly_x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f), p0, p1);
-            } else {
-                p0 = ex2_approx(x0);
-                p1 = ex2_approx(x1);
-            }
+            p0 = ex2_approx(x0);
+            p1 = ex2_approx(x1);
             if (e & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
             else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
             pk[e] = pack_half2(p0, p1);
@@ -429,8 +390,7 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
         float nmc;
         const float alpha = update_max(m, row_max(s), p.scale_log2, nmc);
-        float unused_mx;
-        l = l * alpha + exp_and_store_p<false, false>(s, p.scale_log2, nmc, tS, unused_mx);
+        l = l * alpha + exp_and_store_p(s, p.scale_log2, nmc, tS);
         if (j > 0) rescale_o_row<H>(tO, alpha);  // PV(j-1) finished: BAR_O was waited below
         tmem_wait_st();
         tc_fence_before();
@@ -563,6 +523,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
+#if defined(FA_TRACE) || defined(FA_CYCLES)
+    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512] = static_cast<unsigned long long>(clock64());
+#endif
 
     if (warp < 8) {
         // ------------------------------------------------------------------ softmax, tile i
@@ -587,37 +550,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 float s[kTile];
                 const bool ragged = (j + 1) * kTile > p.L;
                 const bool first = j == 0;
-#if FA_LD_PIPE
-                tmem_ld32(tS, s);
-                tmem_wait_ld_tied(s);
-                tmem_ld32(tS + 32, s + 32);
-                tmem_ld32(tS + 64, s + 64);
-                tmem_ld32(tS + 96, s + 96);
-                if (ragged || first) {   // both need the whole row before the first exponential
-                    tmem_wait_ld_tied(s + 32);
-                    tmem_wait_ld_tied(s + 64);
-                    tmem_wait_ld_tied(s + 96);
-                    if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
-                    if (first) m = row_max(s);   // first key tile: the reference is its row maximum
-                }
-#else
                 load_s_row(tS, s);
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
-                if (first) m = row_max(s);
-#endif
-                if (tr_me) FA_TRACE_EV(1 + i, 2);   // first scores in registers
-                // Part a, chunks [0, FA_SPLIT_P): exponentials against the standing reference, with
+                if (first) m = row_max(s);   // first key tile: the reference is its row maximum
+                if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
+                // Part a, chunks [0, kSplitChunks): exponentials against the standing reference, with
                 // the maximum of these scores taken in the same pass.  The reference only has to
                 // move when a score exceeds it by more than 2^8 in the exp2 domain.
                 {
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     float sum = exp_chunks<0, 1, true>(s, c, -m * c, tS, mx4);
-#if FA_LD_PIPE
-                    tmem_wait_ld_tied(s + 32);
-                    tmem_wait_ld_tied(s + 64);
-                    tmem_wait_ld_tied(s + 96);
-#endif
-                    sum += exp_chunks<1, FA_SPLIT_P, true>(s, c, -m * c, tS, mx4);
+                    sum += exp_chunks<1, kSplitChunks, true>(s, c, -m * c, tS, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -628,7 +571,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
                         float unused[4];
-                        l = l * alpha + exp_chunks<0, FA_SPLIT_P, false>(s, c, -m * c, tS, unused);
+                        l = l * alpha + exp_chunks<0, kSplitChunks, false>(s, c, -m * c, tS, unused);
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -643,11 +586,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
                 if (tr_me) FA_TRACE_EV(1 + i, 4);   // part a of P signalled
-#if FA_SPLIT_P < 4
                 // Part b, the remaining chunks, while the MMA warp already multiplies part a by V.
                 {
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    const float sum = exp_chunks<FA_SPLIT_P, 4, true>(s, c, -m * c, tS, mx4);
+                    const float sum = exp_chunks<kSplitChunks, 4, true>(s, c, -m * c, tS, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -657,7 +599,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
                         float unused[4];
-                        l = l * alpha + exp_chunks<FA_SPLIT_P, 4, false>(s, c, -m * c, tS, unused);
+                        l = l * alpha + exp_chunks<kSplitChunks, 4, false>(s, c, -m * c, tS, unused);
                         mbar_wait(bar(BAR_PVA0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_PVA0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -671,7 +613,6 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (lane == 0) mbar_arrive(bar(BAR_PB0 + i));
                     if (tr_me) FA_TRACE_EV(1 + i, 6);   // part b of P signalled
                 }
-#endif
             }
             // Hand the row sums to the epilogue.  The A barrier may run at most one phase ahead of
             // the epilogue's wait, so the previous item's O must have been read out first (always
@@ -807,14 +748,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
                 FA_TRACE_EV(0, 2);   // P0 ready
                 tc_fence_after();
-                if (leader) issue_pv<H, 0, 2 * FA_SPLIT_P>(tO0, tS0, slot_addr(tv), acc);
-#if FA_SPLIT_P < 4
+                if (leader) issue_pv<H, 0, 2 * kSplitChunks>(tO0, tS0, slot_addr(tv), acc);
                 if (leader) tc_commit(bar(BAR_PVA0));
                 mbar_wait(bar(BAR_PB0), g & 1u, ctl, kRoleMma | BAR_PB0);
                 FA_TRACE_EV(0, 3);   // part b of P0 ready
                 tc_fence_after();
-                if (leader) issue_pv<H, 2 * FA_SPLIT_P, 8>(tO0, tS0, slot_addr(tv), 1u);
-#endif
+                if (leader) issue_pv<H, 2 * kSplitChunks, 8>(tO0, tS0, slot_addr(tv), 1u);
                 if (leader) tc_commit(bar(BAR_PV0));
                 FA_TRACE_EV(0, 8);   // P V of tile 0 issued
                 if (more && leader) {
@@ -830,14 +769,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
                 FA_TRACE_EV(0, 5);   // P1 ready
                 tc_fence_after();
-                if (leader) issue_pv<H, 0, 2 * FA_SPLIT_P>(tO1, tS1, slot_addr(tv), acc);
-#if FA_SPLIT_P < 4
+                if (leader) issue_pv<H, 0, 2 * kSplitChunks>(tO1, tS1, slot_addr(tv), acc);
                 if (leader) tc_commit(bar(BAR_PVA1));
                 mbar_wait(bar(BAR_PB1), g & 1u, ctl, kRoleMma | BAR_PB1);
                 FA_TRACE_EV(0, 6);   // part b of P1 ready
                 tc_fence_after();
-                if (leader) issue_pv<H, 2 * FA_SPLIT_P, 8>(tO1, tS1, slot_addr(tv), 1u);
-#endif
+                if (leader) issue_pv<H, 2 * kSplitChunks, 8>(tO1, tS1, slot_addr(tv), 1u);
                 if (leader) {
                     tc_commit(bar(BAR_PV1));
                     free_slot(tv);
@@ -903,6 +840,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     tc_fence_before();
     __syncthreads();
+#if defined(FA_TRACE) || defined(FA_CYCLES)
+    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512 + 1] = static_cast<unsigned long long>(clock64());
+#endif
     if (warp == 12) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);

@@ -27,26 +27,6 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
-// Named barrier over `n` threads (a multiple of 32) of the CTA; ids 1..15 (0 is __syncthreads).
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t n) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
-}
-// Same barrier, returning the OR of `pred` over all participating threads.
-__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t n, bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %3, 0;\n\t"
-        "bar.red.or.pred p, %1, %2, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(r)
-        : "r"(id), "r"(n), "r"(static_cast<uint32_t>(pred))
-        : "memory");
-    return r != 0;
-}
-
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -186,19 +166,6 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// The same wait, tied to the 32 registers a preceding tcgen05.ld.x32 filled: the compiler can move
-// no use of them above it.  Needed where further loads are issued between the load and the first
-// use of its registers, so that program order alone no longer separates them.
-__device__ __forceinline__ void tmem_wait_ld_tied(float* v) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]),
-                   "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]),
-                   "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]),
-                   "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]),
-                   "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31])
-                 :
-                 : "memory");
-}
 __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -298,10 +265,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
         "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
         "r"(v[15])
-#ifndef FA_ST_NOCLOBBER
-        : "memory"
-#endif
-        );
+        : "memory");
 }
 
 // ----------------------------------------------------------------------------- arithmetic
@@ -331,7 +295,6 @@ __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
 __device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-#ifndef FA_SCALAR_MATH
 __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
@@ -341,43 +304,6 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     uint64_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
-}
-#else  // comparison build: the same interface on scalar instructions
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-    float a0, a1, b0, b1, c0, c1;
-    unpack_f32x2(a, a0, a1); unpack_f32x2(b, b0, b1); unpack_f32x2(c, c0, c1);
-    return pack_f32x2(fmaf(a0, b0, c0), fmaf(a1, b1, c1));
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-    float a0, a1, b0, b1;
-    unpack_f32x2(a, a0, a1); unpack_f32x2(b, b0, b1);
-    return pack_f32x2(a0 + b0, a1 + b1);
-}
-#endif
-
-// mbarrier arrival worth `count` arrivals.
-__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-// 2^x for a pair of fp32 values on the FMA and integer pipes (no MUFU): round-to-nearest split
-// x = n + f with f in [-0.5, 0.5] by the 1.5*2^23 trick, a degree-3 minimax polynomial for 2^f
-// (relative error 7.5e-5, below the 4.9e-4 spacing of the fp16 values P is rounded to), and n added
-// into the exponent field.  Inputs must be >= -125 (callers clamp) and are meaningful up to ~126.
-__device__ __forceinline__ void ex2_poly_x2(float x0, float x1, float& p0, float& p1) {
-    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23
-    const uint64_t x2 = pack_f32x2(x0, x1);
-    const uint64_t t2 = add_f32x2(x2, pack_f32x2(kMagic, kMagic));          // low mantissa bits = n
-    const uint64_t n2 = add_f32x2(t2, pack_f32x2(-kMagic, -kMagic));        // n as float
-    const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), x2);          // f = x - n
-    uint64_t q2 = fma_f32x2(f2, pack_f32x2(0.0551716685f, 0.0551716685f), pack_f32x2(0.2426111251f, 0.2426111251f));
-    q2 = fma_f32x2(q2, f2, pack_f32x2(0.6932609677f, 0.6932609677f));
-    q2 = fma_f32x2(q2, f2, pack_f32x2(0.9999280572f, 0.9999280572f));
-    float q0, q1, t0, t1;
-    unpack_f32x2(q2, q0, q1);
-    unpack_f32x2(t2, t0, t1);
-    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 
 template <int kRegs>

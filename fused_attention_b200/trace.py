@@ -1,12 +1,18 @@
-"""Per-role time line of one CTA of the pipelined kernel.
+"""Per-role time line of one CTA of the pipelined kernel, or its SM clock count.
 
-    python -m fused_attention_b200.trace [--workload NAME] [--cta N]
+    python -m fused_attention_b200.trace [--workload NAME] [--cta N] [--dump STEPS]
+    python -m fused_attention_b200.trace --cycles [--workload NAME]
 
 Builds ``lib/libfa_b200_trace.so`` from the same sources with ``-DFA_TRACE`` (the normal library has
 no tracing code), runs the workload once with one CTA recording ``clock64`` at its hand-over points,
 and prints, in SM clocks: the length of a key step, how long the MMA warp spends issuing each group of
 MMAs and waiting for each P, and how long a softmax warp spends on each part of its step.  This is a
 diagnostic for kernel work; it is not used by the operator, the tests or the benchmark.
+
+``--cycles`` builds ``lib/libfa_b200_cycles.so`` with ``-DFA_CYCLES`` instead: the kernel is the normal one
+plus two clock reads in CTA 0 (start and end of its work).  The count does not depend on the clock the
+GPU happens to run at, which the launch time under the power cap does, so it is the figure to compare
+two versions of the kernel by; the recording code of the time line costs a few per cent itself.
 """
 from __future__ import annotations
 
@@ -19,21 +25,23 @@ import sys
 from . import build as _build
 
 TRACE_LIB = os.path.join(_build.LIBDIR, "libfa_b200_trace.so")
+CYCLES_LIB = os.path.join(_build.LIBDIR, "libfa_b200_cycles.so")
 MMA_TAGS = {1: "V and next K landed", 2: "P0 part a ready", 3: "P0 part b ready", 8: "PV0 issued", 4: "QK0 issued",
             5: "P1 part a ready", 6: "P1 part b ready", 10: "PV1 issued", 7: "QK1 issued"}
 SM_TAGS = {1: "S ready", 2: "S in registers", 5: "part a exponentials issued", 4: "part a signalled",
            6: "part b signalled"}
 
 
-def build_trace_lib(force: bool = False) -> str:
+def build_trace_lib(force: bool = False, cycles_only: bool = False) -> str:
     srcs = _build.lib_sources()
-    if not force and os.path.exists(TRACE_LIB) and all(os.path.getmtime(s) < os.path.getmtime(TRACE_LIB) for s in srcs):
-        return TRACE_LIB
+    out = CYCLES_LIB if cycles_only else TRACE_LIB
+    if not force and os.path.exists(out) and all(os.path.getmtime(s) < os.path.getmtime(out) for s in srcs):
+        return out
     os.makedirs(_build.LIBDIR, exist_ok=True)
-    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DFA_TRACE", *os.environ.get("FA_TRACE_FLAGS", "").split(), "-I", os.path.join(_build.ROOT, "include"), "-I", _build.CSRC,
-           "-o", TRACE_LIB, os.path.join(_build.CSRC, "fa_b200.cu")]
+    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DFA_CYCLES" if cycles_only else "-DFA_TRACE", "-I",
+           os.path.join(_build.ROOT, "include"), "-I", _build.CSRC, "-o", out, os.path.join(_build.CSRC, "fa_b200.cu")]
     subprocess.run(cmd, check=True)
-    return TRACE_LIB
+    return out
 
 
 def _mean(xs):
@@ -45,6 +53,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--cta", type=int, default=20, help="which CTA records (block index)")
+    ap.add_argument("--cycles", action="store_true", help="SM clocks of CTA 0 per launch instead of the time line")
     ap.add_argument("--dump", type=int, default=0, metavar="N",
                     help="also print the merged time line of all roles over N key steps from the middle of the record")
     args = ap.parse_args(argv)
@@ -53,7 +62,7 @@ def main(argv=None) -> int:
     from .workloads import HEADLINE, WORKLOADS, workload_inputs
 
     w = WORKLOADS[args.workload or HEADLINE]
-    lib = ctypes.CDLL(build_trace_lib())
+    lib = ctypes.CDLL(build_trace_lib(cycles_only=args.cycles))
     u32, vp, i32 = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
     lib.fa_b200_attention_forward.restype = i32
     lib.fa_b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
@@ -72,6 +81,24 @@ def main(argv=None) -> int:
     for _ in range(3):
         run()
     torch.cuda.synchronize()
+    if args.cycles:
+        lib.fa_b200_trace_setup(buf.data_ptr(), 0xFFFFFFFF)   # no CTA records a time line; CTA 0 stamps start and end
+        counts = []
+        for _ in range(11):
+            run()
+            torch.cuda.synchronize()
+            t = buf.cpu()
+            counts.append(int(t[7 * 512 + 1] - t[7 * 512]))
+        lib.fa_b200_trace_setup(None, 0)
+        cyc = sorted(counts)[len(counts) // 2]
+        n = (w.L + 127) // 128
+        items = ((w.L + 255) // 256) * w.R * w.B
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        steps = -(-items // min(sms, items)) * n           # key steps of CTA 0
+        mma_clk = steps * 2 * 2 * (128 * 128 * w.H * 2) / 8192   # two tiles x two products, 8192 FLOP per clock and SM
+        print(f"workload {w.name}: {cyc} SM clocks per launch in CTA 0 (median of {len(counts)}), {steps} key steps, "
+              f"{cyc / steps:.0f} clocks per key step; the MMAs alone need {mma_clk / steps:.0f}: tensor pipe busy {100 * mma_clk / cyc:.1f} %")
+        return 0
     lib.fa_b200_trace_setup(buf.data_ptr(), args.cta)
     run()
     torch.cuda.synchronize()
