@@ -192,11 +192,6 @@ __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const 
     return lo + hi;
 }
 
-// The pipelined kernel's softmax hands P of a key tile to the MMA warp in two parts: the first
-// kSplitChunks chunks of 32 keys, then the rest with a second arrival, so that P V starts while the
-// last exponentials are still being taken.  Measured: 3 beats 2 and 4 (the whole row at once).
-constexpr int kSplitChunks = 3;
-
 // P = exp2(s*c + nmc) for the 32-key chunks [kC0, kC1) of one score row, written as fp16 into TMEM
 // at tP + 16*chunk (two values per column, even key index in the low half); returns the fp32 sum of
 // those P.  With kWithMax the running maxima mx[] take in the scores of these chunks in the same
@@ -433,6 +428,17 @@ struct PipeCfg {
     static constexpr uint32_t kTmemCols = 512;
     // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+H) O1 [384,384+H)
     static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+    // At H = 64 the O tiles leave 2 x 64 columns free: P gets columns of its own, [320,384) and
+    // [448,512), instead of overwriting its S.  The next Q K^T of a tile then no longer has to wait
+    // for the P V that reads P, only for the softmax warps to have read S, and a tile's softmax
+    // passes follow one another without the MMAs in between.  At H = 128 all 512 columns are taken.
+    static constexpr bool kSeparateP = H == 64;
+    static constexpr uint32_t kColP0 = kSeparateP ? 320 : kColS0, kColP1 = kSeparateP ? 448 : kColS1;
+    // The softmax hands P of a key tile to the MMA warp in two parts: the first kSplit chunks of 32
+    // keys, then the rest with a second arrival, so that P V starts while the last exponentials are
+    // still being taken and leaves the chain S -> P -> P V -> next S earlier.  Measured at H = 128:
+    // 3 beats 2 and 4 (the whole row at once).  With P in its own columns there is no such chain.
+    static constexpr int kSplit = kSeparateP ? 4 : 3;
 };
 
 // Persistent: grid = min(number of SMs, work items), block = 512.  A work item is one pair of
@@ -468,6 +474,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_PB0, BAR_PB1,            // softmax -> MMA: part b of P written (4 arrivals)
         BAR_PVA0, BAR_PVA1,          // MMA -> softmax: P V of part a complete (waited for only in the
                                      // rare steps whose reference moves within part b)
+        BAR_SFREE0, BAR_SFREE1,      // softmax -> MMA: S read into registers (4 arrivals); only used
+                                     // when P has columns of its own
         BAR_PV0, BAR_PV1,            // MMA -> softmax (rescale steps) and epilogue: P V complete
         BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
         BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
@@ -505,6 +513,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
             const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_PB0 || i == BAR_PB1 ||
+                                   i == BAR_SFREE0 || i == BAR_SFREE1 ||
                                    i == BAR_A0 || i == BAR_A1 ||
                                    i == BAR_OFREE0 || i == BAR_OFREE1);
             mbar_init(bar(i), per_warp ? 4u : 1u);
@@ -534,6 +543,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t row = tid & 127u;
         const uint32_t lane_off = ((warp & 3u) * 32u) << 16;
         const uint32_t tS = tmem_base + lane_off + (i ? C::kColS1 : C::kColS0);
+        const uint32_t tP = tmem_base + lane_off + (i ? C::kColP1 : C::kColP0);
         const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
         const float c = p.scale_log2;
         FA_TRACE_DECL
@@ -551,16 +561,27 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const bool ragged = (j + 1) * kTile > p.L;
                 const bool first = j == 0;
                 load_s_row(tS, s);
+                if constexpr (C::kSeparateP) {
+                    // S is in registers: the MMA warp may overwrite it with the next step's scores.
+                    // P has one buffer per tile: the previous step's P V must have read it.
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(BAR_SFREE0 + i));
+                    if (g > 0) {
+                        mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                        tc_fence_after();
+                    }
+                }
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
                 if (first) m = row_max(s);   // first key tile: the reference is its row maximum
                 if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
-                // Part a, chunks [0, kSplitChunks): exponentials against the standing reference, with
+                // Part a, chunks [0, C::kSplit): exponentials against the standing reference, with
                 // the maximum of these scores taken in the same pass.  The reference only has to
                 // move when a score exceeds it by more than 2^8 in the exp2 domain.
                 {
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    float sum = exp_chunks<0, 1, true>(s, c, -m * c, tS, mx4);
-                    sum += exp_chunks<1, kSplitChunks, true>(s, c, -m * c, tS, mx4);
+                    float sum = exp_chunks<0, 1, true>(s, c, -m * c, tP, mx4);
+                    sum += exp_chunks<1, C::kSplit, true>(s, c, -m * c, tP, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -571,7 +592,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
                         float unused[4];
-                        l = l * alpha + exp_chunks<0, kSplitChunks, false>(s, c, -m * c, tS, unused);
+                        l = l * alpha + exp_chunks<0, C::kSplit, false>(s, c, -m * c, tP, unused);
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -587,9 +608,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
                 if (tr_me) FA_TRACE_EV(1 + i, 4);   // part a of P signalled
                 // Part b, the remaining chunks, while the MMA warp already multiplies part a by V.
-                {
+                if constexpr (C::kSplit < 4) {
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    const float sum = exp_chunks<kSplitChunks, 4, true>(s, c, -m * c, tS, mx4);
+                    const float sum = exp_chunks<C::kSplit, 4, true>(s, c, -m * c, tP, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -599,7 +620,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
                         float unused[4];
-                        l = l * alpha + exp_chunks<kSplitChunks, 4, false>(s, c, -m * c, tS, unused);
+                        l = l * alpha + exp_chunks<C::kSplit, 4, false>(s, c, -m * c, tP, unused);
                         mbar_wait(bar(BAR_PVA0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_PVA0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -699,6 +720,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const bool leader = elect_one();
             const uint32_t tS0 = tmem_base + C::kColS0, tS1 = tmem_base + C::kColS1;
             const uint32_t tO0 = tmem_base + C::kColO0, tO1 = tmem_base + C::kColO1;
+            const uint32_t tP0 = tmem_base + C::kColP0, tP1 = tmem_base + C::kColP1;
             auto slot_addr = [&](uint32_t t) { return sRing + (t % NS) * G::kTileBytes; };
             auto wait_full = [&](uint32_t t) {
                 mbar_wait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
@@ -731,63 +753,117 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
             uint32_t k = 0, j = 0;   // item and key step of global step g
-            for (uint32_t g = 0; g < steps; ++g) {
-                const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
-                const bool more = g + 1 < steps;          // a next global step exists
-                const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
-                const uint32_t acc = j > 0 ? 1u : 0u;
-                // everything of this step lands long before P is ready: keep these waits off the path
-                wait_full(tv);
-                if (more) {
-                    wait_full(tk);
-                    if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+            if constexpr (C::kSeparateP) {
+                // P in columns of its own: per tile, the next step's Q K^T goes out as soon as the
+                // softmax warps have read S, ahead of the P V of this step.
+                for (uint32_t g = 0; g < steps; ++g) {
+                    const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
+                    const bool more = g + 1 < steps;          // a next global step exists
+                    const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
+                    const uint32_t acc = j > 0 ? 1u : 0u;
+                    wait_full(tv);
+                    if (more) {
+                        wait_full(tk);
+                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                    }
+                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                    // tile 0
+                    if (more) {
+                        mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                        tc_fence_after();
+                        if (leader) {
+                            issue_qk<H>(tS0, sQ, slot_addr(tk));
+                            tc_commit(bar(BAR_S0));
+                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+                        }
+                    }
+                    mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                    tc_fence_after();
+                    if (leader) {
+                        issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
+                        tc_commit(bar(BAR_PV0));
+                    }
+                    // tile 1
+                    if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                    if (more) {
+                        mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        tc_fence_after();
+                        if (leader) {
+                            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                            tc_commit(bar(BAR_S1));
+                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
+                            free_slot(tk);
+                        }
+                    }
+                    mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                    tc_fence_after();
+                    if (leader) {
+                        issue_pv<H>(tO1, tP1, slot_addr(tv), acc);
+                        tc_commit(bar(BAR_PV1));
+                        free_slot(tv);
+                    }
+                    if (++j == n) { j = 0; ++k; }
                 }
-                if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
-                FA_TRACE_EV(0, 1);   // V and next K landed
-                // tile 0
-                mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
-                FA_TRACE_EV(0, 2);   // P0 ready
-                tc_fence_after();
-                if (leader) issue_pv<H, 0, 2 * kSplitChunks>(tO0, tS0, slot_addr(tv), acc);
-                if (leader) tc_commit(bar(BAR_PVA0));
-                mbar_wait(bar(BAR_PB0), g & 1u, ctl, kRoleMma | BAR_PB0);
-                FA_TRACE_EV(0, 3);   // part b of P0 ready
-                tc_fence_after();
-                if (leader) issue_pv<H, 2 * kSplitChunks, 8>(tO0, tS0, slot_addr(tv), 1u);
-                if (leader) tc_commit(bar(BAR_PV0));
-                FA_TRACE_EV(0, 8);   // P V of tile 0 issued
-                if (more && leader) {
-                    issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
-                    tc_commit(bar(BAR_S0));
-                    // the Q K^T of an item's last key step is its last use of the query tile
-                    if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+            } else {
+                for (uint32_t g = 0; g < steps; ++g) {
+                    const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
+                    const bool more = g + 1 < steps;          // a next global step exists
+                    const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
+                    const uint32_t acc = j > 0 ? 1u : 0u;
+                    // everything of this step lands long before P is ready: keep these waits off the path
+                    wait_full(tv);
+                    if (more) {
+                        wait_full(tk);
+                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                    }
+                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                    FA_TRACE_EV(0, 1);   // V and next K landed
+                    // tile 0
+                    mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                    FA_TRACE_EV(0, 2);   // P0 ready
+                    tc_fence_after();
+                    if (leader) issue_pv<H, 0, 2 * C::kSplit>(tO0, tP0, slot_addr(tv), acc);
+                    if (leader) tc_commit(bar(BAR_PVA0));
+                    mbar_wait(bar(BAR_PB0), g & 1u, ctl, kRoleMma | BAR_PB0);
+                    FA_TRACE_EV(0, 3);   // part b of P0 ready
+                    tc_fence_after();
+                    if (leader) issue_pv<H, 2 * C::kSplit, 8>(tO0, tP0, slot_addr(tv), 1u);
+                    if (leader) tc_commit(bar(BAR_PV0));
+                    FA_TRACE_EV(0, 8);   // P V of tile 0 issued
+                    if (more && leader) {
+                        issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
+                        tc_commit(bar(BAR_S0));
+                        // the Q K^T of an item's last key step is its last use of the query tile
+                        if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+                    }
+                    FA_TRACE_EV(0, 4);   // tile 0 MMAs issued
+                    // tile 1
+                    if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                    mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                    FA_TRACE_EV(0, 5);   // P1 ready
+                    tc_fence_after();
+                    if (leader) issue_pv<H, 0, 2 * C::kSplit>(tO1, tP1, slot_addr(tv), acc);
+                    if (leader) tc_commit(bar(BAR_PVA1));
+                    mbar_wait(bar(BAR_PB1), g & 1u, ctl, kRoleMma | BAR_PB1);
+                    FA_TRACE_EV(0, 6);   // part b of P1 ready
+                    tc_fence_after();
+                    if (leader) issue_pv<H, 2 * C::kSplit, 8>(tO1, tP1, slot_addr(tv), 1u);
+                    if (leader) {
+                        tc_commit(bar(BAR_PV1));
+                        free_slot(tv);
+                    }
+                    FA_TRACE_EV(0, 10);  // P V of tile 1 issued
+                    if (more && leader) {
+                        issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                        tc_commit(bar(BAR_S1));
+                        if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
+                        free_slot(tk);
+                    }
+                    FA_TRACE_EV(0, 7);   // tile 1 MMAs issued
+                    if (++j == n) { j = 0; ++k; }
                 }
-                FA_TRACE_EV(0, 4);   // tile 0 MMAs issued
-                // tile 1
-                if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
-                mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
-                FA_TRACE_EV(0, 5);   // P1 ready
-                tc_fence_after();
-                if (leader) issue_pv<H, 0, 2 * kSplitChunks>(tO1, tS1, slot_addr(tv), acc);
-                if (leader) tc_commit(bar(BAR_PVA1));
-                mbar_wait(bar(BAR_PB1), g & 1u, ctl, kRoleMma | BAR_PB1);
-                FA_TRACE_EV(0, 6);   // part b of P1 ready
-                tc_fence_after();
-                if (leader) issue_pv<H, 2 * kSplitChunks, 8>(tO1, tS1, slot_addr(tv), 1u);
-                if (leader) {
-                    tc_commit(bar(BAR_PV1));
-                    free_slot(tv);
-                }
-                FA_TRACE_EV(0, 10);  // P V of tile 1 issued
-                if (more && leader) {
-                    issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
-                    tc_commit(bar(BAR_S1));
-                    if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
-                    free_slot(tk);
-                }
-                FA_TRACE_EV(0, 7);   // tile 1 MMAs issued
-                if (++j == n) { j = 0; ++k; }
             }
             if (leader) tc_commit(bar(BAR_FINAL));
             __syncwarp();

@@ -244,8 +244,17 @@ def test_host_buffer_entry_point_matches_device_entry_point():
     m1[:, :, 500:] = float("-inf")
     assert torch.equal(run(q1, k1, v1, 128, mask=m1), fa.attention_forward_host(128, 128, q1, k1, v1, m1).float())
     # many batch entries: more entries than chunks
-    q2, k2, v2 = make_inputs(11, 130, 64, 1.0, 23)
+    q2, k2, v2 = make_inputs(41, 130, 64, 1.0, 23)
     assert torch.equal(run(q2, k2, v2, 32), fa.attention_forward_host(32, 32, q2, k2, v2).float())
+    # large enough to be cut into groups of heads per batch entry (pitched copies), uneven groups, with and without mask
+    q3, k3, v3 = make_inputs(2, 1100, 7 * 128, 1.0, 24)
+    assert torch.equal(run(q3, k3, v3, 128), fa.attention_forward_host(128, 128, q3, k3, v3).float())
+    m3 = torch.zeros(2, 1100, 1100, dtype=torch.float16)
+    m3[0, :, 900:] = float("-inf")
+    m3[1, :, :100] = float("-inf")
+    assert torch.equal(run(q3, k3, v3, 128, mask=m3), fa.attention_forward_host(128, 128, q3, k3, v3, m3).float())
+    q4, k4, v4 = make_inputs(1, 2048, 16 * 64, 1.0, 25)
+    assert torch.equal(run(q4, k4, v4, 64), fa.attention_forward_host(64, 64, q4, k4, v4).float())
 
 
 def test_concurrent_callers_from_several_threads():
