@@ -755,39 +755,59 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             uint32_t k = 0, j = 0;   // item and key step of global step g
             if constexpr (C::kSeparateP) {
                 // P in columns of its own: per tile, the next step's Q K^T goes out as soon as the
-                // softmax warps have read S, ahead of the P V of this step.
+                // softmax warps have read S, ahead of the P V of this step.  The tiles that have landed
+                // and the S that has been read are known long before the MMA warp needs to know, so
+                // those barriers are tested ahead of a group of MMAs and the answer is read after it
+                // (mbar_poll_begin); only the waits for P block.
+                mbar_poll_declare();
+                bool polled = false;   // predicates 0-2 hold answers for this step
                 for (uint32_t g = 0; g < steps; ++g) {
                     const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
                     const bool more = g + 1 < steps;          // a next global step exists
                     const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
                     const uint32_t acc = j > 0 ? 1u : 0u;
-                    wait_full(tv);
-                    if (more) {
-                        wait_full(tk);
-                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                    {
+                        uint32_t ok_v = 0, ok_k = 0, ok_s0 = 0;
+                        if (polled) {
+                            ok_v = mbar_poll_end<0>();
+                            ok_k = mbar_poll_end<1>();
+                            ok_s0 = mbar_poll_end<2>();
+                        }
+                        if (!ok_v) wait_full(tv);
+                        if (more) {
+                            if (!ok_k) wait_full(tk);
+                            if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                            if (!ok_s0) mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                        }
                     }
                     if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                    FA_TRACE_EV(0, 1);   // V and next K landed, S0 read by the softmax warps
                     // tile 0
                     if (more) {
-                        mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
                         tc_fence_after();
                         if (leader) {
                             issue_qk<H>(tS0, sQ, slot_addr(tk));
                             tc_commit(bar(BAR_S0));
+                            // the Q K^T of an item's last key step is its last use of the query tile
                             if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
                         }
                     }
+                    FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
                     mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                    FA_TRACE_EV(0, 2);   // P0 ready
                     tc_fence_after();
+                    if (more) mbar_poll_begin<3>(bar(BAR_SFREE1), g & 1u);   // read behind the P V below
                     if (leader) {
                         issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
                         tc_commit(bar(BAR_PV0));
                     }
+                    FA_TRACE_EV(0, 8);   // P V of tile 0 issued
                     // tile 1
                     if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
                     if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
                     if (more) {
-                        mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        if (!mbar_poll_end<3>()) mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
                         tc_fence_after();
                         if (leader) {
                             issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
@@ -796,13 +816,24 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             free_slot(tk);
                         }
                     }
+                    FA_TRACE_EV(0, 7);   // next Q K^T of tile 1 issued
                     mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                    FA_TRACE_EV(0, 5);   // P1 ready
                     tc_fence_after();
+                    // what the next step starts with: test now, read at the top of the next step
+                    polled = more;
+                    if (more) {
+                        const uint32_t nv = tv + 2, nk = tk + 2;
+                        mbar_poll_begin<0>(bar(BAR_FULL + (nv % NS)), (nv / NS) & 1u);
+                        mbar_poll_begin<1>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
+                        mbar_poll_begin<2>(bar(BAR_SFREE0), (g + 1u) & 1u);
+                    }
                     if (leader) {
                         issue_pv<H>(tO1, tP1, slot_addr(tv), acc);
                         tc_commit(bar(BAR_PV1));
                         free_slot(tv);
                     }
+                    FA_TRACE_EV(0, 10);  // P V of tile 1 issued
                     if (++j == n) { j = 0; ++k; }
                 }
             } else {

@@ -55,6 +55,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Deferred barrier test for the thread that issues tcgen05.mma.  A shared-memory result reaches that
+// thread only behind the MMAs it has queued (150 to 300 clocks during which it issues nothing), even
+// when the phase it asks about completed long ago.  For barriers that are known to complete early it
+// therefore asks ahead of a group of MMAs and looks at the answer after issuing them:
+//   mbar_poll_declare()        once, at the top of the role's code (declares the predicate registers)
+//   mbar_poll_begin<N>(...)    mbarrier.test_wait into predicate N; nothing waits for the result yet
+//   ... issue a group of MMAs ...
+//   mbar_poll_end<N>()         reads predicate N: non-zero if the phase was complete when tested
+// The predicates are PTX registers of function scope shared by these pieces of inline assembly, since
+// inline assembly cannot hand a predicate to C++.
+__device__ __forceinline__ void mbar_poll_declare() {
+    asm volatile(".reg .pred fa_poll0, fa_poll1, fa_poll2, fa_poll3;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void mbar_poll_begin(uint32_t bar, uint32_t parity) {
+    static_assert(N >= 0 && N < 4, "four predicates are declared");
+    if (N == 0) asm volatile("mbarrier.test_wait.parity.shared::cta.b64 fa_poll0, [%0], %1;" ::"r"(bar), "r"(parity) : "memory");
+    if (N == 1) asm volatile("mbarrier.test_wait.parity.shared::cta.b64 fa_poll1, [%0], %1;" ::"r"(bar), "r"(parity) : "memory");
+    if (N == 2) asm volatile("mbarrier.test_wait.parity.shared::cta.b64 fa_poll2, [%0], %1;" ::"r"(bar), "r"(parity) : "memory");
+    if (N == 3) asm volatile("mbarrier.test_wait.parity.shared::cta.b64 fa_poll3, [%0], %1;" ::"r"(bar), "r"(parity) : "memory");
+}
+template <int N>
+__device__ __forceinline__ uint32_t mbar_poll_end() {
+    uint32_t ok;
+    if (N == 0) asm volatile("selp.u32 %0, 1, 0, fa_poll0;" : "=r"(ok)::"memory");
+    if (N == 1) asm volatile("selp.u32 %0, 1, 0, fa_poll1;" : "=r"(ok)::"memory");
+    if (N == 2) asm volatile("selp.u32 %0, 1, 0, fa_poll2;" : "=r"(ok)::"memory");
+    if (N == 3) asm volatile("selp.u32 %0, 1, 0, fa_poll3;" : "=r"(ok)::"memory");
+    return ok;
+}
+
 // Where a bounded wait reports: a device status word pair and a CTA-wide abort flag.
 struct WaitCtl {
     uint32_t* status;              // global: [0] first failure code, [1] number of reporting CTAs

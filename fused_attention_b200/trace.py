@@ -27,7 +27,8 @@ from . import build as _build
 TRACE_LIB = os.path.join(_build.LIBDIR, "libfa_b200_trace.so")
 CYCLES_LIB = os.path.join(_build.LIBDIR, "libfa_b200_cycles.so")
 MMA_TAGS = {1: "V and next K landed", 2: "P0 part a ready", 3: "P0 part b ready", 8: "PV0 issued", 4: "QK0 issued",
-            5: "P1 part a ready", 6: "P1 part b ready", 10: "PV1 issued", 7: "QK1 issued"}
+            5: "P1 part a ready", 6: "P1 part b ready", 10: "PV1 issued", 7: "QK1 issued",
+            11: "S0 read by softmax", 12: "S1 read by softmax"}
 SM_TAGS = {1: "S ready", 2: "S in registers", 5: "part a exponentials issued", 4: "part a signalled",
            6: "part b signalled"}
 
@@ -117,8 +118,15 @@ def main(argv=None) -> int:
     ev = {name: [(x >> 8, x & 255) for x in t[s].tolist() if x] for s, name in slots.items()}
     n = max(1, (w.L + 127) // 128)
     mma = ev["mma"]
-    ends = [c for c, g in mma if g == 7]
+    # a key step ends with the last group the MMA warp issues in it: the next Q K^T of tile 1, or, at
+    # head_dim 64 where that goes out ahead of P V, the P V of tile 1
+    end_tag = 10 if w.H == 64 else 7
+    ends = [c for c, g in mma if g == end_tag]
     periods = [b - a for a, b in zip(ends, ends[1:])]
+    if not periods:
+        print("no key steps recorded (does the chosen CTA have work?); events per role:",
+              {name: len(e) for name, e in ev.items()}, "MMA tags:", sorted({g for _, g in mma}))
+        return 1
     steady = sorted(periods)[: max(1, len(periods) * 3 // 4)]          # drop the item-boundary steps
     print(f"key steps per item: {n}; clocks per key step: median of the steady ones {steady[len(steady) // 2]}, "
           f"all {periods[:24]}")
