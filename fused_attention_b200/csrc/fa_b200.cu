@@ -138,8 +138,12 @@ int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask,
     // as soon as there are enough items to occupy a good part of the SMs (measured: 39 vs 57 us on
     // B=64 R=16 L=197 H=64); a single partial tile or a handful of items goes to the simple kernel,
     // which has twice as many, smaller CTAs.
+    // With few items the two are level up to about five key steps (7-14 us, mostly launch); from
+    // there on the pipelined kernel wins however few items there are (measured: B=1 R=16 L=1024 H=128
+    // 20.5 vs 24.6 us, B=1 R=4 L=2048 32.8 vs 41.9 us, B=1 R=2 L=4096 57 vs 79 us).
     const uint64_t pairs = static_cast<uint64_t>((L + 255) / 256) * (F / H) * B;
     if (L <= 128) return 1;
+    if (L > 5 * 128) return 2;
     if (pairs * 2 < static_cast<uint64_t>(sm_count)) return 1;
     return 2;
 }

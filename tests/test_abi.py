@@ -96,7 +96,8 @@ def test_kernel_selection(lib):
     assert sel(1, 256, 256, 64, 0, 0) == 1         # tiny: simple
     assert sel(64, 197, 1024, 64, 0, 0) == 2       # 1024 items of two key steps: persistent kernel
     assert sel(64, 100, 1024, 64, 0, 0) == 1       # a single partial tile per (batch, head)
-    assert sel(1, 2048, 512, 128, 0, 0) == 1       # 32 items cannot occupy the SMs
+    assert sel(1, 2048, 512, 128, 0, 0) == 2       # 32 items only, but 16 key steps each: pipelined
+    assert sel(1, 512, 512, 128, 0, 0) == 1        # 8 items of 4 key steps cannot occupy the SMs
     assert sel(4, 2048, 512, 16, 0, 0) == 1        # small head_dim
     assert sel(4, 2048, 4096, 128, 1, 0) == 1      # mask
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_FORCE_SIMPLE) == 1
