@@ -306,6 +306,27 @@ def test_non_default_stream_and_output_placement():
     assert torch.equal(y, fa.attention_forward(128, 64, q, k, v))
 
 
+@pytest.mark.parametrize("H,L,R", [(64, 256, 4), (128, 1000, 3)])
+def test_operator_can_be_recorded_in_a_cuda_graph(H, L, R):
+    """After one ordinary call on the device (which does the once-per-device set-up), a call neither
+    allocates nor synchronises: it can be recorded in a CUDA graph and replayed on new input values."""
+    q, k, v = (t.cuda() for t in make_inputs(2, L, R * H, 1.0, 31))
+    fa.attention_forward(H, 32, q, k, v)                    # set-up outside the recording
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = fa.attention_forward(H, 32, q, k, v)
+    q2, k2, v2 = make_inputs(2, L, R * H, 1.0, 32)
+    for dst, src in ((q, q2), (k, k2), (v, v2)):
+        dst.copy_(src)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert_close(y.float().cpu(), oracle(q2, k2, v2, H))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, fa.attention_forward(H, 32, q, k, v))
+
+
 def test_error_behaviour_on_gpu_tensors():
     q, k, v = (t.cuda() for t in make_inputs(1, 64, 128, 1.0, 41))
     with pytest.raises(RuntimeError):
