@@ -5,7 +5,7 @@
 //                               order.  Covers every head_dim (16, 32, 64, 128), the additive mask
 //                               and tiny problems; several CTAs per SM overlap one another.
 //   fa_fwd_pipelined<H>         two 128-row query tiles per CTA, 512 threads split into roles
-//                               (2 softmax warpgroups, 1 correction warpgroup, 1 MMA warp, 1 TMA
+//                               (2 softmax warpgroups, 1 epilogue warpgroup, 1 MMA warp, 1 TMA
 //                               warp); K/V stream through a shared-memory ring; the softmax of one
 //                               tile overlaps the MMAs of the other.  H in {64, 128}, no mask.
 //
@@ -22,8 +22,9 @@
 // That layout is the canonical K-major operand (Q and K for S = Q K^T) and, read with the
 // MN-major bit set, the canonical operand for V in O = P V, so V is never transposed.
 //
-// TMEM (columns of 128 lanes x 32 bit): S tile 128 columns of fp32; P (fp16, two per column)
-// overwrites the first 64 columns of its S; O tile H columns of fp32.
+// TMEM (columns of 128 lanes x 32 bit): S tile 128 columns of fp32; P (fp16, two per column) 64
+// columns; O tile H columns of fp32.  P overwrites the first 64 columns of its S, except in the
+// pipelined kernel at H = 64, where two 64-column O tiles leave room for P columns of its own.
 #pragma once
 
 #include <cuda.h>
@@ -75,7 +76,7 @@ enum : uint32_t {
     kRoleProducer = 0x200u,
     kRoleMma = 0x300u,
     kRoleSoftmax = 0x400u,
-    kRoleCorrection = 0x500u,
+    kRoleEpilogue = 0x500u,
     kRoleDrain = 0x600u
 };
 
@@ -661,12 +662,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (uint32_t i = 0; i < 2; ++i) {
                 // this wait lasts for a whole item: poll every 100 ns
-                mbar_wait_relaxed(bar(BAR_A0 + i), k & 1u, ctl, kRoleCorrection | (BAR_A0 + i), 100);
+                mbar_wait_relaxed(bar(BAR_A0 + i), k & 1u, ctl, kRoleEpilogue | (BAR_A0 + i), 100);
                 const float inv_l = 1.f / l_buf[k & 1u][i][row];
                 // The item's last P V of this tile.  Every earlier phase of this barrier has
                 // completed by the time the softmax warps signalled and the next phase needs this
                 // epilogue's OFREE arrival, so the parity test is unambiguous.
-                mbar_wait(bar(BAR_PV0 + i), (k * n + n - 1u) & 1u, ctl, kRoleCorrection | (BAR_PV0 + i));
+                mbar_wait(bar(BAR_PV0 + i), (k * n + n - 1u) & 1u, ctl, kRoleEpilogue | (BAR_PV0 + i));
                 tc_fence_after();
                 __syncwarp();
                 const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
