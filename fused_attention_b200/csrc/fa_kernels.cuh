@@ -23,8 +23,8 @@
 // MN-major bit set, the canonical operand for V in O = P V, so V is never transposed.
 //
 // TMEM (columns of 128 lanes x 32 bit): S tile 128 columns of fp32; P (fp16, two per column) 64
-// columns; O tile H columns of fp32.  P overwrites the first 64 columns of its S, except in the
-// pipelined kernel at H = 64, where two 64-column O tiles leave room for P columns of its own.
+// columns; O tile H columns of fp32.  In the simple kernel P overwrites the first 64 columns of
+// its S; in the pipelined kernel P has columns of its own (PipeCfg).
 #pragma once
 
 #include <cuda.h>
@@ -197,9 +197,11 @@ __device__ __forceinline__ float exp_and_store_p(const float (&s)[kTile], const 
 // at tP + 16*chunk (two values per column, even key index in the low half); returns the fp32 sum of
 // those P.  With kWithMax the running maxima mx[] take in the scores of these chunks in the same
 // pass (the maximum instructions fill the issue slots the MUFU leaves free).
-template <int kC0, int kC1, bool kWithMax>
+// With kStore false the packed P are not written to TMEM but handed back in pk_out (16 words per
+// chunk), for the caller to store once the P buffer is free.
+template <int kC0, int kC1, bool kWithMax, bool kStore = true>
 __device__ __forceinline__ float exp_chunks(const float (&s)[kTile], const float c, const float nmc,
-                                            const uint32_t tP, float (&mx)[4]) {
+                                            const uint32_t tP, float (&mx)[4], uint32_t* pk_out = nullptr) {
     const uint64_t c2 = pack_f32x2(c, c), n2 = pack_f32x2(nmc, nmc);
     uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
@@ -217,7 +219,12 @@ __device__ __forceinline__ float exp_chunks(const float (&s)[kTile], const float
             pk[e] = pack_half2(p0, p1);
             if (kWithMax) mx[e & 3] = max3(mx[e & 3], s0, s1);
         }
-        tmem_st16(tP + chunk * 16, pk);
+        if (kStore) {
+            tmem_st16(tP + chunk * 16, pk);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) pk_out[(chunk - kC0) * 16 + e] = pk[e];
+        }
     }
     float lo, hi;
     unpack_f32x2(add_f32x2(sum_a, sum_b), lo, hi);
@@ -428,18 +435,23 @@ struct PipeCfg {
     static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
     // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+H) O1 [384,384+H)
-    static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
-    // At H = 64 the O tiles leave 2 x 64 columns free: P gets columns of its own, [320,384) and
-    // [448,512), instead of overwriting its S.  The next Q K^T of a tile then no longer has to wait
-    // for the P V that reads P, only for the softmax warps to have read S, and a tile's softmax
-    // passes follow one another without the MMAs in between.  At H = 128 all 512 columns are taken.
-    static constexpr bool kSeparateP = H == 64;
-    static constexpr uint32_t kColP0 = kSeparateP ? 320 : kColS0, kColP1 = kSeparateP ? 448 : kColS1;
-    // The softmax hands P of a key tile to the MMA warp in two parts: the first kSplit chunks of 32
-    // keys, then the rest with a second arrival, so that P V starts while the last exponentials are
-    // still being taken and leaves the chain S -> P -> P V -> next S earlier.  Measured at H = 128:
-    // 3 beats 2 and 4 (the whole row at once).  With P in its own columns there is no such chain.
-    static constexpr int kSplit = kSeparateP ? 4 : 3;
+    // P (fp16, 64 columns per tile) has columns of its own instead of overwriting its S: the next
+    // Q K^T of a tile then does not have to wait for the P V that reads P, only for the softmax warps
+    // to have read S, and a tile's softmax passes follow one another without its MMAs in between.
+    //   H = 64:   S0 [0,128)  S1 [128,256)  O0 [256,320)  P0 [320,384)  O1 [384,448)  P1 [448,512)
+    //   H = 128:  S  [0,128) shared by the two tiles, which use it in turn (scores only live from the
+    //             Q K^T until the softmax warps have read them), P0 [128,192)  P1 [192,256)
+    //             O0 [256,384)  O1 [384,512)
+    static constexpr bool kSharedS = H == 128;
+    static constexpr uint32_t kColS0 = 0, kColS1 = kSharedS ? 0 : 128, kColO0 = 256, kColO1 = 384;
+    static constexpr uint32_t kColP0 = kSharedS ? 128 : 320, kColP1 = kSharedS ? 192 : 448;
+    // Two MMA-issuing warps (one for Q K^T, one for P V) or one for both.  Measured: two win at
+    // H = 128 (-3 % SM clocks), one, with its early barriers tested ahead, at H = 64 (-5 %).
+    static constexpr bool kTwoIssuers = H == 128;
+    // How many 32-key chunks of exponentials a softmax thread takes into registers before it needs
+    // the P buffer to be free of the previous step's P V.  Measured at H = 128: 1 (-2.4 %; 2 and 3
+    // spill); at H = 64 holding any back costs more than it hides.
+    static constexpr int kHeldChunks = H == 128 ? 1 : 0;
 };
 
 // Persistent: grid = min(number of SMs, work items), block = 512.  A work item is one pair of
@@ -451,10 +463,18 @@ struct PipeCfg {
 //
 // warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1 (each also rescales its O rows in
 // the rare steps whose reference maximum moves); 8-11: epilogue (Y = O / l);
-// 12: MMA issue (one elected lane) and TMEM owner; 13: TMA producer (one lane); 14-15: idle.
+// 12: MMA issue (one elected lane) and TMEM owner; 13: TMA producer (one lane); 14: second MMA
+// issuing warp at H = 128 (12 issues Q K^T, 14 issues P V); 15: idle.
+//
+// Per tile and key step: Q K^T -> S; the softmax warps read S into registers and say so (SFREE),
+// which lets the next Q K^T into the S buffer; they write P into the tile's P columns once the
+// previous step's P V has read them (PV); P V accumulates into O.  Nothing of a tile's next Q K^T
+// waits for its P V.
 //
 // Barrier phases (the parity to wait for is the low bit of the index):
-//   per global step g = k*n + j:  S_i (MMA -> softmax), P_i (softmax -> MMA), PV_i (MMA -> all)
+//   per global step g = k*n + j:  S_i (MMA -> softmax), SFREE (softmax -> MMA; at H = 128 one
+//                barrier whose phase is the use 2g + i of the shared S buffer), P_i (softmax -> MMA),
+//                PV_i (MMA -> softmax and, for the item's last step, epilogue)
 //   per item k:  QFULL_i (TMA -> MMA), QEMPTY_i (MMA -> TMA), A_i (softmax -> epilogue),
 //                OFREE_i (epilogue -> MMA and softmax)
 //   per ring item t (K0 V0 K1 V1 ... across items):  FULL[t % NS], EMPTY[t % NS]
@@ -472,15 +492,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
         BAR_P0, BAR_P1,              // softmax -> MMA: P written (and O rescaled in the rare steps
                                      // that need it); 4 arrivals, one per softmax warp
-        BAR_PB0, BAR_PB1,            // softmax -> MMA: part b of P written (4 arrivals)
-        BAR_PVA0, BAR_PVA1,          // MMA -> softmax: P V of part a complete (waited for only in the
-                                     // rare steps whose reference moves within part b)
-        BAR_SFREE0, BAR_SFREE1,      // softmax -> MMA: S read into registers (4 arrivals); only used
-                                     // when P has columns of its own
-        BAR_PV0, BAR_PV1,            // MMA -> softmax (rescale steps) and epilogue: P V complete
+        BAR_SFREE0, BAR_SFREE1,      // softmax -> MMA: S read into registers (4 arrivals); with the
+                                     // one S buffer of H = 128 only the first, one phase per use
+        BAR_PV0, BAR_PV1,            // MMA -> softmax (P buffer free, O at rest) and epilogue: P V complete
         BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
         BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
+        BAR_FINAL2,                  // the same for the second issuing warp
         BAR_FULL,                    // NS ring barriers TMA -> MMA
         BAR_EMPTY = BAR_FULL + NS,   // NS ring barriers MMA -> TMA
         BAR_COUNT = BAR_EMPTY + NS
@@ -513,8 +531,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < BAR_COUNT; ++i) {
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
-            const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_PB0 || i == BAR_PB1 ||
-                                   i == BAR_SFREE0 || i == BAR_SFREE1 ||
+            const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_SFREE0 || i == BAR_SFREE1 ||
                                    i == BAR_A0 || i == BAR_A1 ||
                                    i == BAR_OFREE0 || i == BAR_OFREE1);
             mbar_init(bar(i), per_warp ? 4u : 1u);
@@ -562,12 +579,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const bool ragged = (j + 1) * kTile > p.L;
                 const bool first = j == 0;
                 load_s_row(tS, s);
-                if constexpr (C::kSeparateP) {
-                    // S is in registers: the MMA warp may overwrite it with the next step's scores.
-                    // P has one buffer per tile: the previous step's P V must have read it.
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(BAR_SFREE0 + i));
+                // S is in registers: the MMA warp may overwrite it with the next scores.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(C::kSharedS ? BAR_SFREE0 : BAR_SFREE0 + static_cast<int>(i)));
+                // P has one buffer per tile: the previous step's P V must have read it before it is
+                // written again.  Where no exponentials are held back in registers the wait is here.
+                if constexpr (C::kHeldChunks == 0) {
                     if (g > 0) {
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
@@ -576,25 +594,37 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
                 if (first) m = row_max(s);   // first key tile: the reference is its row maximum
                 if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
-                // Part a, chunks [0, C::kSplit): exponentials against the standing reference, with
-                // the maximum of these scores taken in the same pass.  The reference only has to
-                // move when a score exceeds it by more than 2^8 in the exp2 domain.
+                // Exponentials against the standing reference, with the maximum of the scores taken
+                // in the same pass.  The reference only has to move when a score exceeds it by more
+                // than 2^8 in the exp2 domain.  P has one buffer per tile and the previous step's P V
+                // may still be reading it: the first chunks' exponentials go to registers meanwhile.
                 {
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    float sum = exp_chunks<0, 1, true>(s, c, -m * c, tP, mx4);
-                    sum += exp_chunks<1, C::kSplit, true>(s, c, -m * c, tP, mx4);
+                    uint32_t held[16 * (C::kHeldChunks > 0 ? C::kHeldChunks : 1)];
+                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, -m * c, tP, mx4, held);
+                    if constexpr (C::kHeldChunks > 0) {
+                        if (g > 0) {
+                            mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                            tc_fence_after();
+                        }
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
+                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, -m * c, tP, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
                         // Some row of this warp needs a new reference: redo the warp's exponentials
-                        // (rows that keep theirs reproduce the same P) and rescale O by alpha once
-                        // the previous step's P V has retired.
+                        // (rows that keep theirs reproduce the same P) and rescale O by alpha; the
+                        // previous step's P V has retired (waited for above), so O is at rest.
                         const float m_new = moved ? mx : m;
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
                         float unused[4];
-                        l = l * alpha + exp_chunks<0, C::kSplit, false>(s, c, -m * c, tP, unused);
-                        mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                        l = l * alpha + exp_chunks<0, 4, false>(s, c, -m * c, tP, unused);
+                        // (This wait returns at once.  It is here because with a branch point at this
+                        // place of the rare path the compiler allocates the common path without spills.)
+                        if (g > 0) mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
                         rescale_o_row<H>(tO, alpha);
@@ -602,39 +632,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         l += sum;
                     }
                 }
-                if (tr_me) FA_TRACE_EV(1 + i, 5);   // part a's exponentials issued
+                if (tr_me) FA_TRACE_EV(1 + i, 5);   // exponentials issued
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
-                if (tr_me) FA_TRACE_EV(1 + i, 4);   // part a of P signalled
-                // Part b, the remaining chunks, while the MMA warp already multiplies part a by V.
-                if constexpr (C::kSplit < 4) {
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    const float sum = exp_chunks<C::kSplit, 4, true>(s, c, -m * c, tP, mx4);
-                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                    const bool moved = (mx - m) * c > kLazyRescaleLog2;
-                    if (__any_sync(0xffffffffu, moved)) {
-                        // The new reference shows up in part b only: O (which by now takes in part a
-                        // against the old reference) is rescaled once part a's P V has retired.
-                        const float m_new = moved ? mx : m;
-                        const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
-                        m = m_new;
-                        float unused[4];
-                        l = l * alpha + exp_chunks<C::kSplit, 4, false>(s, c, -m * c, tP, unused);
-                        mbar_wait(bar(BAR_PVA0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_PVA0 + i));
-                        tc_fence_after();
-                        __syncwarp();
-                        rescale_o_row<H>(tO, alpha);
-                    } else {
-                        l += sum;
-                    }
-                    tmem_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(BAR_PB0 + i));
-                    if (tr_me) FA_TRACE_EV(1 + i, 6);   // part b of P signalled
-                }
+                if (tr_me) FA_TRACE_EV(1 + i, 4);   // P signalled
             }
             // Hand the row sums to the epilogue.  The A barrier may run at most one phase ahead of
             // the epilogue's wait, so the previous item's O must have been read out first (always
@@ -714,10 +717,14 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) bulk_wait_all();   // Y is complete before the CTA leaves
     } else {
         setmaxnreg_dec<80>();
-        if (warp == 12) {
+        if (warp == 12 || (C::kTwoIssuers && warp == 14)) {
             // -------------------------------------------------------------- MMA issue
             // The whole warp walks the loop (uniform control flow keeps descriptors in uniform
-            // registers); one elected lane issues the MMAs and commits.
+            // registers); one elected lane issues the MMAs and commits.  With P in columns of its
+            // own, warp 12 issues the Q K^T of both tiles and warp 14 their P V: the two streams
+            // depend on nothing of one another (different TMEM columns, different ring slots), and
+            // a barrier wait of one issuing thread, which costs it 150-300 clocks during which it
+            // issues nothing, is then covered by the MMAs the other warp has queued.
             const bool leader = elect_one();
             const uint32_t tS0 = tmem_base + C::kColS0, tS1 = tmem_base + C::kColS1;
             const uint32_t tO0 = tmem_base + C::kColO0, tO1 = tmem_base + C::kColO1;
@@ -734,7 +741,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
             const uint32_t steps = my_items * n;   // global steps of this CTA
             // ring item 2g is the K tile of global step g, item 2g+1 its V tile
-            if (steps > 0) {
+            if (steps > 0 && warp == 12) {
                 // S tiles of the very first step
                 mbar_wait(bar(BAR_QFULL0), 0, ctl, kRoleMma | BAR_QFULL0);
                 wait_full(0);
@@ -745,6 +752,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (n == 1) tc_commit(bar(BAR_QEMPTY0));
                 }
                 mbar_wait(bar(BAR_QFULL1), 0, ctl, kRoleMma | BAR_QFULL1);
+                // one S buffer for both tiles: tile 0's scores must have been read first
+                if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 0, ctl, kRoleMma | BAR_SFREE0);
                 tc_fence_after();
                 if (leader) {
                     issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
@@ -754,7 +763,86 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
             uint32_t k = 0, j = 0;   // item and key step of global step g
-            if constexpr (C::kSeparateP) {
+            if constexpr (C::kTwoIssuers) {
+                mbar_poll_declare();
+                bool polled = false;
+                if (warp == 12) {
+                    // Q K^T stream: for every step g the scores of step g + 1, tile 0 then tile 1, each
+                    // as soon as the softmax warps have read what the S buffer holds.  That K has
+                    // landed is known long before; it is tested ahead of the previous step's last
+                    // MMAs and the answer read after them (mbar_poll_begin).
+                    for (uint32_t g = 0; g + 1 < steps; ++g) {
+                        const uint32_t tk = 2 * g + 2;
+                        const bool next_new_item = j + 1 == n;    // step g + 1 opens item k + 1
+                        if (!(polled && mbar_poll_end<0>())) wait_full(tk);
+                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                        // With one S buffer its uses are numbered 2g + i (tile i, step g) and use u
+                        // needs the reading of use u - 1 (one barrier, phase = use); with one buffer
+                        // per tile the reading of step g of that tile.
+                        if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 1u, ctl, kRoleMma | BAR_SFREE0);
+                        else mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                        FA_TRACE_EV(0, 11);  // S0 read by the softmax warps
+                        tc_fence_after();
+                        if (leader) {
+                            issue_qk<H>(tS0, sQ, slot_addr(tk));
+                            tc_commit(bar(BAR_S0));
+                            // the Q K^T of an item's last key step is its last use of the query tile
+                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+                        }
+                        FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
+                        if (next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                        if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 0u, ctl, kRoleMma | BAR_SFREE0);
+                        else mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
+                        tc_fence_after();
+                        polled = g + 2 < steps;
+                        if (polled) {
+                            const uint32_t nk = tk + 2;
+                            mbar_poll_begin<0>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
+                        }
+                        if (leader) {
+                            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                            tc_commit(bar(BAR_S1));
+                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
+                            free_slot(tk);
+                        }
+                        FA_TRACE_EV(0, 7);   // next Q K^T of tile 1 issued
+                        if (++j == n) { j = 0; ++k; }
+                    }
+                } else {
+                    // P V stream: for every step the products of tile 0 and tile 1 as their P arrive.
+                    for (uint32_t g = 0; g < steps; ++g) {
+                        const uint32_t tv = 2 * g + 1;
+                        const uint32_t acc = j > 0 ? 1u : 0u;
+                        if (!(polled && mbar_poll_end<1>())) wait_full(tv);
+                        if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                        mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                        FA_TRACE_EV(3, 2);   // P0 ready
+                        tc_fence_after();
+                        if (leader) {
+                            issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
+                            tc_commit(bar(BAR_PV0));
+                        }
+                        FA_TRACE_EV(3, 8);   // P V of tile 0 issued
+                        if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                        mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                        FA_TRACE_EV(3, 5);   // P1 ready
+                        tc_fence_after();
+                        polled = g + 1 < steps;
+                        if (polled) {
+                            const uint32_t nv = tv + 2;
+                            mbar_poll_begin<1>(bar(BAR_FULL + (nv % NS)), (nv / NS) & 1u);
+                        }
+                        if (leader) {
+                            issue_pv<H>(tO1, tP1, slot_addr(tv), acc);
+                            tc_commit(bar(BAR_PV1));
+                            free_slot(tv);
+                        }
+                        FA_TRACE_EV(3, 10);  // P V of tile 1 issued
+                        if (++j == n) { j = 0; ++k; }
+                    }
+                }
+            } else {
                 // P in columns of its own: per tile, the next step's Q K^T goes out as soon as the
                 // softmax warps have read S, ahead of the P V of this step.  The tiles that have landed
                 // and the S that has been read are known long before the MMA warp needs to know, so
@@ -837,69 +925,11 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     FA_TRACE_EV(0, 10);  // P V of tile 1 issued
                     if (++j == n) { j = 0; ++k; }
                 }
-            } else {
-                for (uint32_t g = 0; g < steps; ++g) {
-                    const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
-                    const bool more = g + 1 < steps;          // a next global step exists
-                    const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
-                    const uint32_t acc = j > 0 ? 1u : 0u;
-                    // everything of this step lands long before P is ready: keep these waits off the path
-                    wait_full(tv);
-                    if (more) {
-                        wait_full(tk);
-                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
-                    }
-                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
-                    FA_TRACE_EV(0, 1);   // V and next K landed
-                    // tile 0
-                    mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
-                    FA_TRACE_EV(0, 2);   // P0 ready
-                    tc_fence_after();
-                    if (leader) issue_pv<H, 0, 2 * C::kSplit>(tO0, tP0, slot_addr(tv), acc);
-                    if (leader) tc_commit(bar(BAR_PVA0));
-                    mbar_wait(bar(BAR_PB0), g & 1u, ctl, kRoleMma | BAR_PB0);
-                    FA_TRACE_EV(0, 3);   // part b of P0 ready
-                    tc_fence_after();
-                    if (leader) issue_pv<H, 2 * C::kSplit, 8>(tO0, tP0, slot_addr(tv), 1u);
-                    if (leader) tc_commit(bar(BAR_PV0));
-                    FA_TRACE_EV(0, 8);   // P V of tile 0 issued
-                    if (more && leader) {
-                        issue_qk<H>(tS0, sQ, slot_addr(tk));  // in order behind the P V that reads P0
-                        tc_commit(bar(BAR_S0));
-                        // the Q K^T of an item's last key step is its last use of the query tile
-                        if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
-                    }
-                    FA_TRACE_EV(0, 4);   // tile 0 MMAs issued
-                    // tile 1
-                    if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
-                    mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
-                    FA_TRACE_EV(0, 5);   // P1 ready
-                    tc_fence_after();
-                    if (leader) issue_pv<H, 0, 2 * C::kSplit>(tO1, tP1, slot_addr(tv), acc);
-                    if (leader) tc_commit(bar(BAR_PVA1));
-                    mbar_wait(bar(BAR_PB1), g & 1u, ctl, kRoleMma | BAR_PB1);
-                    FA_TRACE_EV(0, 6);   // part b of P1 ready
-                    tc_fence_after();
-                    if (leader) issue_pv<H, 2 * C::kSplit, 8>(tO1, tP1, slot_addr(tv), 1u);
-                    if (leader) {
-                        tc_commit(bar(BAR_PV1));
-                        free_slot(tv);
-                    }
-                    FA_TRACE_EV(0, 10);  // P V of tile 1 issued
-                    if (more && leader) {
-                        issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
-                        tc_commit(bar(BAR_S1));
-                        if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
-                        free_slot(tk);
-                    }
-                    FA_TRACE_EV(0, 7);   // tile 1 MMAs issued
-                    if (++j == n) { j = 0; ++k; }
-                }
             }
-            if (leader) tc_commit(bar(BAR_FINAL));
+            const int bar_final = warp == 12 ? BAR_FINAL : BAR_FINAL2;
+            if (leader) tc_commit(bar(bar_final));
             __syncwarp();
-            mbar_wait(bar(BAR_FINAL), 0, ctl, kRoleMma | BAR_FINAL);
+            mbar_wait(bar(bar_final), 0, ctl, kRoleMma | static_cast<uint32_t>(bar_final));
         } else if (warp == 13 && elect_one()) {
             // -------------------------------------------------------------- TMA producer
             uint32_t t = 0;           // ring item

@@ -26,11 +26,10 @@ from . import build as _build
 
 TRACE_LIB = os.path.join(_build.LIBDIR, "libfa_b200_trace.so")
 CYCLES_LIB = os.path.join(_build.LIBDIR, "libfa_b200_cycles.so")
-MMA_TAGS = {1: "V and next K landed", 2: "P0 part a ready", 3: "P0 part b ready", 8: "PV0 issued", 4: "QK0 issued",
-            5: "P1 part a ready", 6: "P1 part b ready", 10: "PV1 issued", 7: "QK1 issued",
-            11: "S0 read by softmax", 12: "S1 read by softmax"}
-SM_TAGS = {1: "S ready", 2: "S in registers", 5: "part a exponentials issued", 4: "part a signalled",
-           6: "part b signalled"}
+MMA_TAGS = {1: "V and next K landed", 2: "P0 ready", 8: "PV0 issued", 4: "next QK0 issued",
+            5: "P1 ready", 10: "PV1 issued", 7: "next QK1 issued",
+            11: "S buffer free for tile 0", 12: "S buffer free for tile 1"}
+SM_TAGS = {1: "S ready", 2: "S in registers", 5: "exponentials issued", 4: "P signalled"}
 
 
 def build_trace_lib(force: bool = False, cycles_only: bool = False) -> str:
@@ -114,14 +113,15 @@ def main(argv=None) -> int:
     print(f"workload {w.name}: {ms * 1e3:.1f} us per launch, {w.flops / ms / 1e9:.1f} TFLOP/s (trace build)")
 
     t = buf.cpu().view(8, 512)
-    slots = {0: "mma", 1: "softmax0", 2: "softmax1"}
+    slots = {0: "mma", 1: "softmax0", 2: "softmax1", 3: "mma_pv"}
     ev = {name: [(x >> 8, x & 255) for x in t[s].tolist() if x] for s, name in slots.items()}
     n = max(1, (w.L + 127) // 128)
-    mma = ev["mma"]
-    # a key step ends with the last group the MMA warp issues in it: the next Q K^T of tile 1, or, at
-    # head_dim 64 where that goes out ahead of P V, the P V of tile 1
-    end_tag = 10 if w.H == 64 else 7
-    ends = [c for c, g in mma if g == end_tag]
+    # where P has TMEM columns of its own a second warp issues the P V (slot 3); its stamps are read
+    # together with those of the first
+    mma = sorted(ev["mma"] + ev.pop("mma_pv"))
+    ev["mma"] = mma
+    # one stamp per key step: the P V of tile 1 issued
+    ends = [c for c, g in mma if g == 10]
     periods = [b - a for a, b in zip(ends, ends[1:])]
     if not periods:
         print("no key steps recorded (does the chosen CTA have work?); events per role:",
