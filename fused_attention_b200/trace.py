@@ -54,6 +54,9 @@ def main(argv=None) -> int:
     ap.add_argument("--workload", default=None)
     ap.add_argument("--cta", type=int, default=20, help="which CTA records (block index)")
     ap.add_argument("--cycles", action="store_true", help="SM clocks of CTA 0 per launch instead of the time line")
+    ap.add_argument("--dump-from", type=int, default=-1, metavar="STEP",
+                    help="first key step of the dump (default: the middle of the record); an item of the headline "
+                         "workload has 16 key steps, so 14 shows an item boundary")
     ap.add_argument("--dump", type=int, default=0, metavar="N",
                     help="also print the merged time line of all roles over N key steps from the middle of the record")
     args = ap.parse_args(argv)
@@ -147,7 +150,7 @@ def main(argv=None) -> int:
             if len(vals) >= 4:
                 print(f"  {SM_TAGS.get(g0, g0):>22} -> {SM_TAGS.get(g1, g1):<22} {_mean(vals):7.0f}")
     if args.dump > 0 and len(ends) > args.dump + 4:
-        mid = len(ends) // 2
+        mid = args.dump_from if 0 <= args.dump_from < len(ends) - args.dump else len(ends) // 2
         lo, hi = ends[mid], ends[mid + args.dump]
         merged = sorted((c, name, g) for name, e in ev.items() for c, g in e if lo <= c <= hi)
         print(f"merged time line of {args.dump} key steps (clocks from the first event):")
