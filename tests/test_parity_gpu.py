@@ -116,6 +116,40 @@ def test_seeded_random_shapes(H, B, R, L, flags, sigma):
     assert m["max_abs"] <= MAX_ABS_TOL * scale and m["mean_abs"] <= MEAN_ABS_TOL * scale, m
 
 
+@pytest.mark.parametrize("seed", [1, 2])
+def test_many_random_shapes_against_fp32_attention_on_the_device(seed):
+    """200 shapes per seed (lengths to 5000, up to 40 heads, key spikes that move the reference maximum
+    late in a tile) through the pipelined kernel; the checker here is fp32 torch attention on the same GPU
+    because the CPU oracle would need minutes at these sizes. Tolerance: the absolute bound for unit-scale
+    values, times sigma, plus one fp16 rounding of the output value itself; results must repeat bit for bit."""
+    import random
+    rng = random.Random(seed)
+    failures = []
+    for it in range(200):
+        H = rng.choice([64, 128])
+        B = rng.randint(1, 6)
+        R = rng.randint(1, 40)
+        L = rng.choice([rng.randint(1, 300), rng.randint(300, 1500), rng.randint(1500, 5000)])
+        if B * R * L * L > 3e9:
+            R = max(1, int(3e9 / (B * L * L)))
+        sigma = rng.choice([0.3, 1.0, 2.5])
+        g = torch.Generator(device="cuda")
+        g.manual_seed(1000 * seed + it)
+        q, k, v = ((torch.randn(B, L, R * H, generator=g, device="cuda") * sigma).half() for _ in range(3))
+        if rng.random() < 0.3:
+            pos = rng.randrange(L)
+            k[:, pos, :] = 3.0 * q[:, rng.randrange(L), :].sign()
+        y = fa.attention_forward(H, 32, q, k, v, flags=PIPE)
+        y2 = fa.attention_forward(H, 32, q, k, v, flags=PIPE)
+        qf, kf, vf = (t.float().view(B, L, R, H).transpose(1, 2) for t in (q, k, v))
+        ref = (torch.softmax(qf @ kf.mT / H ** 0.5, -1) @ vf).transpose(1, 2).reshape(B, L, R * H)
+        d = (y.float() - ref).abs()
+        excess = (d - (MAX_ABS_TOL * max(1.0, sigma) + ref.abs() * 2.0 ** -10)).max().item()
+        if not (torch.isfinite(y).all().item() and excess <= 0 and torch.equal(y, y2)):
+            failures.append((H, B, R, L, sigma, d.max().item()))
+    assert not failures, failures
+
+
 def test_many_batches_and_heads_index_correctly():
     # every (batch, head) pair gets its own inputs; a wrong offset shows as a large error
     q, k, v = make_inputs(5, 200, 7 * 64, 1.0, 77)
