@@ -158,6 +158,35 @@ def test_many_batches_and_heads_index_correctly():
         assert_close(run(q, k, v, 64, flags=flags), expected)
 
 
+@pytest.mark.parametrize("flags", [PIPE, SIMPLE])
+def test_tensors_larger_than_four_gib(flags):
+    """Q, K, V and Y of 4.25 GiB each: the last batch entries lie beyond a 32-bit byte offset and the very
+    last one beyond a 32-bit element offset (the reference indexes with 32-bit offsets,
+    include/fused_attn.cuh:685-686, and cannot take this shape).  A batch entry of the big call must equal,
+    bit for bit, the same entry computed alone, and that one is checked against fp32 attention."""
+    B, L, F = 17, 4096, 32768                  # 17 * 4096 * 32768 = 2^31 + 2^27 elements
+    H = 128 if flags == PIPE else 64
+    R = F // H
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4242)
+    q, k, v = (torch.empty(B, L, F, dtype=torch.float16, device="cuda") for _ in range(3))
+    for t in (q, k, v):
+        for b in range(B):                     # filled entry by entry: no fp32 temporary of the whole tensor
+            t[b] = torch.randn(L, F, generator=g, device="cuda", dtype=torch.float16)
+    y = fa.attention_forward(H, 32 if H == 128 else 16, q, k, v, flags=flags)
+    for b in (0, 8, B - 1):
+        alone = fa.attention_forward(H, 32 if H == 128 else 16, q[b:b + 1], k[b:b + 1], v[b:b + 1], flags=flags)
+        assert torch.equal(y[b], alone[0]), b
+    b = B - 1
+    for h in (0, R // 2, R - 1):               # heads at both ends of the last entry against fp32 attention
+        qf, kf, vf = (t[b, :, h * H:(h + 1) * H].float() for t in (q, k, v))
+        ref = torch.softmax(qf @ kf.T / H ** 0.5, -1) @ vf
+        d = (y[b, :, h * H:(h + 1) * H].float() - ref).abs()
+        assert d.max().item() <= MAX_ABS_TOL and d.mean().item() <= MEAN_ABS_TOL, (h, d.max().item())
+    del q, k, v, y
+    torch.cuda.empty_cache()
+
+
 @pytest.mark.parametrize("B,R,L,H", [(40, 8, 100, 64), (40, 8, 200, 64), (20, 10, 300, 128), (3, 100, 130, 64),
                                      (2, 160, 257, 128)])
 def test_persistent_kernel_with_several_items_per_cta(B, R, L, H):
