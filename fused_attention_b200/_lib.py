@@ -41,6 +41,7 @@ FLAG_DEFAULT = 0
 FLAG_FORCE_SIMPLE = 1
 FLAG_FORCE_PIPELINED = 2
 FLAG_SYNC = 4
+FLAG_NO_OVERLAP = 8
 
 _lock = threading.Lock()
 _lib = None

@@ -121,7 +121,8 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(y);
     if (all & 15u) return FA_B200_ERR_ALIGNMENT;
     if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return FA_B200_ERR_ALIGNMENT;
-    const uint32_t known = FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_SYNC;
+    const uint32_t known = FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_SYNC |
+                           FA_B200_FLAG_NO_OVERLAP;
     if (flags & ~known) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && (mask || H < 64)) return FA_B200_ERR_FLAGS;
@@ -148,9 +149,28 @@ int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask,
     return 2;
 }
 
+// Launch with or without the programmatic-stream-serialization attribute.  With it the kernel's
+// CTAs may become resident while the previous kernel of the stream drains; the kernels wait for
+// that kernel's completion (griddepcontrol.wait) before they touch global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t st,
+                          bool overlap, const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int H, bool M>
 int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
-                  const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+                  const CUtensorMap& mv, const Params& p, cudaStream_t st, bool overlap) {
     constexpr int smem = 3 * fa::TileGeom<H>::kTileBytes + 1024;
     auto kern = fa::fa_fwd_simple<H, M>;
     if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
@@ -159,13 +179,13 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
         c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
     const dim3 grid((p.L + fa::kTile - 1) / fa::kTile, p.F / H, p.B);
-    kern<<<grid, 128, smem, st>>>(mq, mk, mv, p);
-    return static_cast<int>(cudaGetLastError());
+    const cudaError_t e = launch_kernel(kern, grid, 128, smem, st, overlap, mq, mk, mv, p);
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 template <int H>
 int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
-                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, cudaStream_t st) {
+                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, cudaStream_t st, bool overlap) {
     constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
     auto kern = fa::fa_fwd_pipelined<H>;
     if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
@@ -175,8 +195,8 @@ int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtens
     }
     const uint32_t sms = static_cast<uint32_t>(c.sm_count);
     const dim3 grid(p.n_items < sms ? p.n_items : sms, 1, 1);   // persistent: one CTA per SM
-    kern<<<grid, 512, smem, st>>>(mq, mk, mv, my, p);
-    return static_cast<int>(cudaGetLastError());
+    const cudaError_t e = launch_kernel(kern, grid, 512, smem, st, overlap, mq, mk, mv, my, p);
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // Device-pointer launch on `st`.  Caller holds no lock.
@@ -221,26 +241,27 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.trace_cta = g_trace_cta;
 #endif
                 const int which = select_kernel(B, L, F, H, mask != nullptr, flags, c->sm_count);
+                const bool overlap = (flags & FA_B200_FLAG_NO_OVERLAP) == 0;
                 if (which == 2) {
                     // Y as a TMA store target: boxes of 32 rows x 64 columns (one epilogue warp each)
                     CUtensorMap my;
                     rc = make_map(&my, y, B, L, F, H, 32);
                     if (rc == FA_B200_OK)
-                        rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, my, p, st)
-                                      : launch_pipelined<64>(*c, 9, mq, mk, mv, my, p, st);
+                        rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, my, p, st, overlap)
+                                      : launch_pipelined<64>(*c, 9, mq, mk, mv, my, p, st, overlap);
                 } else if (mask) {
                     switch (H) {
-                        case 16: rc = launch_simple<16, true>(*c, 4, mq, mk, mv, p, st); break;
-                        case 32: rc = launch_simple<32, true>(*c, 5, mq, mk, mv, p, st); break;
-                        case 64: rc = launch_simple<64, true>(*c, 6, mq, mk, mv, p, st); break;
-                        default: rc = launch_simple<128, true>(*c, 7, mq, mk, mv, p, st); break;
+                        case 16: rc = launch_simple<16, true>(*c, 4, mq, mk, mv, p, st, overlap); break;
+                        case 32: rc = launch_simple<32, true>(*c, 5, mq, mk, mv, p, st, overlap); break;
+                        case 64: rc = launch_simple<64, true>(*c, 6, mq, mk, mv, p, st, overlap); break;
+                        default: rc = launch_simple<128, true>(*c, 7, mq, mk, mv, p, st, overlap); break;
                     }
                 } else {
                     switch (H) {
-                        case 16: rc = launch_simple<16, false>(*c, 0, mq, mk, mv, p, st); break;
-                        case 32: rc = launch_simple<32, false>(*c, 1, mq, mk, mv, p, st); break;
-                        case 64: rc = launch_simple<64, false>(*c, 2, mq, mk, mv, p, st); break;
-                        default: rc = launch_simple<128, false>(*c, 3, mq, mk, mv, p, st); break;
+                        case 16: rc = launch_simple<16, false>(*c, 0, mq, mk, mv, p, st, overlap); break;
+                        case 32: rc = launch_simple<32, false>(*c, 1, mq, mk, mv, p, st, overlap); break;
+                        case 64: rc = launch_simple<64, false>(*c, 2, mq, mk, mv, p, st, overlap); break;
+                        default: rc = launch_simple<128, false>(*c, 3, mq, mk, mv, p, st, overlap); break;
                     }
                 }
             }
@@ -479,8 +500,10 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
                                  static_cast<const __half*>(v)};
         // every chunk runs the kernel the whole problem would get, so the result has the same
         // bits as one device-pointer call on the full tensors
+        // (plain launches: a chunk's kernel is ordered behind copies on other streams, not behind a kernel)
         const uint32_t chunk_flags =
             (flags & ~static_cast<uint32_t>(FA_B200_FLAG_SYNC | FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED)) |
+            FA_B200_FLAG_NO_OVERLAP |
             (select_kernel(B, L, F, H, mask_or_null != nullptr, flags, c->sm_count) == 2 ? FA_B200_FLAG_FORCE_PIPELINED
                                                                                        : FA_B200_FLAG_FORCE_SIMPLE);
         if (mbytes && !by_batch) {   // the mask is shared by all heads: one copy ahead of everything

@@ -345,6 +345,10 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Everything above touched only this CTA's own state.  From here on global memory is read and
+    // written: the kernel before this one in the stream must have completed.
+    grid_dep_wait();
+    grid_dep_launch();
     const uint32_t tmem_base = tmem_slot;
     const uint32_t lane_off = (warp * 32u) << 16;
     const uint32_t tS = tmem_base + lane_off;          // this thread's score row
@@ -549,6 +553,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Barriers, TMEM and descriptors are set up; nothing of global memory has been touched yet.  In a
+    // launch that was allowed to overlap the previous kernel of the stream, wait here for that kernel
+    // to complete, then let the next launch's CTAs take the SMs this grid's CTAs leave (they will
+    // stop at this same point: the overlap is never deeper than one launch).
+    grid_dep_wait();
+    grid_dep_launch();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
 #if defined(FA_TRACE) || defined(FA_CYCLES)
     if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512] = static_cast<unsigned long long>(clock64());

@@ -144,6 +144,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl
     return mbar_wait_slow(bar, parity, ctl, code);
 }
 
+// ----------------------------------------------------------------------------- launch overlap
+// Programmatic dependent launch.  A kernel launched with the "programmatic stream serialization"
+// attribute may become resident while the kernel before it in the stream is still running;
+// grid_dep_wait() then blocks until that kernel has completed and its writes are visible (it
+// returns at once in a launch without the attribute).  grid_dep_launch() tells the scheduler that
+// the kernel after this one may be made resident as SMs fall free; it fires once every CTA of
+// this grid has executed it.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -44,8 +44,14 @@ enum {
     FA_B200_FLAG_DEFAULT = 0u,
     FA_B200_FLAG_FORCE_SIMPLE = 1u,    /* always use the one-tile-per-CTA kernel                */
     FA_B200_FLAG_FORCE_PIPELINED = 2u, /* always use the warp-specialised kernel (H in {64,128}) */
-    FA_B200_FLAG_SYNC = 4u             /* synchronise the stream before returning and fold the
+    FA_B200_FLAG_SYNC = 4u,            /* synchronise the stream before returning and fold the
                                           device status word into the return value             */
+    FA_B200_FLAG_NO_OVERLAP = 8u       /* plain launch.  By default the kernel is launched with the
+                                          programmatic-stream-serialization attribute: its CTAs may
+                                          become resident and set up their barriers and tensor memory
+                                          while the previous kernel of the stream drains; they touch
+                                          global memory only once that kernel has completed, so the
+                                          stream's ordering guarantees are unchanged             */
 };
 
 /*

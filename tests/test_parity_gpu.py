@@ -248,6 +248,30 @@ def test_kernels_agree_and_are_deterministic():
     assert float((a - c).abs().max()) <= 1e-3
 
 
+@pytest.mark.parametrize("H,L,flags", [(128, 700, PIPE), (64, 300, PIPE), (64, 100, SIMPLE), (32, 200, SIMPLE)])
+def test_overlapped_launches_keep_the_order_of_the_stream(H, L, flags):
+    """By default a launch may become resident while the previous kernel of the stream drains.  A chain of
+    launches in which each one reads what the one before wrote (Y of step i is V of step i + 1, with no
+    synchronisation in between) must give the bits of the same chain run with plain launches, and a kernel
+    of another library between two launches must be ordered as well."""
+    q, k, v = (t.cuda() for t in make_inputs(3, L, 4 * H, 1.0, 31))
+    chunk = 32 if H == 128 else 16
+
+    def chain(extra):
+        cur = v
+        for step in range(12):
+            cur = fa.attention_forward(H, chunk, q, k, cur, flags=flags | extra)
+            if step % 4 == 3:
+                cur = cur * 2            # a foreign kernel in the middle of the chain
+        torch.cuda.synchronize()
+        return cur
+
+    overlapped = chain(0)
+    plain = chain(_lib.FLAG_NO_OVERLAP)
+    assert torch.equal(overlapped, plain)
+    assert torch.isfinite(overlapped).all()
+
+
 @pytest.mark.parametrize("H", [16, 64, 128])
 @pytest.mark.parametrize("L", [64, 200, 300])
 def test_additive_mask(H, L):
