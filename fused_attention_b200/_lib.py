@@ -42,6 +42,7 @@ FLAG_FORCE_SIMPLE = 1
 FLAG_FORCE_PIPELINED = 2
 FLAG_SYNC = 4
 FLAG_NO_OVERLAP = 8
+FLAG_NO_SPLIT = 16
 
 _lock = threading.Lock()
 _lib = None

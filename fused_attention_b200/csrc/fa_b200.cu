@@ -24,11 +24,12 @@ using fa::Params;
 
 constexpr int kMaxDevices = 64;
 constexpr int kHostChunks = 8;   // pipeline depth of the host-buffer entry point
+constexpr int kStatusWords = 4;  // device status block, see fa::WaitCtl
 
 struct DeviceCtx {
     bool ready = false;
     int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
-    uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count}
+    uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count, id of the launch that reported, -}
     std::atomic<uint32_t> attr_done{0};   // bit per kernel instance whose smem attribute is set
     // host-buffer entry point: copy-in / compute / copy-out streams, per-chunk events and
     // grow-on-demand staging buffers
@@ -41,6 +42,24 @@ struct DeviceCtx {
 
 DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mu;
+std::atomic<uint32_t> g_launch_id{0};   // every launch gets its own non-zero id (Params::launch_id)
+
+uint32_t next_launch_id() {
+    uint32_t id = g_launch_id.fetch_add(1, std::memory_order_relaxed) + 1u;
+    if (id == 0) id = g_launch_id.fetch_add(1, std::memory_order_relaxed) + 1u;
+    return id;
+}
+
+// Read the device status block after the stream has been synchronised; a report is cleared once it
+// has been returned, so that it is given to one caller and later calls start clean.
+int fold_status(uint32_t* status_dev) {
+    uint32_t w[2] = {0, 0};
+    cudaError_t e = cudaMemcpy(w, status_dev, sizeof(w), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (w[0] == 0) return FA_B200_OK;
+    e = cudaMemset(status_dev, 0, 2 * sizeof(uint32_t));
+    return e != cudaSuccess ? static_cast<int>(e) : FA_B200_ERR_DEVICE_TIMEOUT;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -65,9 +84,9 @@ int ensure_ctx(int device, DeviceCtx** out) {
         c.cc_minor = prop.minor;
         c.sm_count = prop.multiProcessorCount;
         c.smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
-        e = cudaMalloc(reinterpret_cast<void**>(&c.status), 2 * sizeof(uint32_t));
+        e = cudaMalloc(reinterpret_cast<void**>(&c.status), kStatusWords * sizeof(uint32_t));
         if (e != cudaSuccess) return static_cast<int>(e);
-        e = cudaMemset(c.status, 0, 2 * sizeof(uint32_t));
+        e = cudaMemset(c.status, 0, kStatusWords * sizeof(uint32_t));
         if (e != cudaSuccess) return static_cast<int>(e);
         c.ready = true;
     }
@@ -115,14 +134,15 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
         if (chunk == 16 && H == 128) return FA_B200_ERR_CHUNK;
     }
     if (B == 0 || L == 0 || F == 0 || F % H != 0) return FA_B200_ERR_SHAPE;
-    if (B > 65535u || F / H > 65535u || L > (1u << 30)) return FA_B200_ERR_SHAPE;  // grid y/z limits
-    if (static_cast<uint64_t>((L + 255) / 256) * (F / H) * B > 0xFFFFFFFFull) return FA_B200_ERR_SHAPE;
+    if (L > (1u << 30)) return FA_B200_ERR_SHAPE;
+    // one CTA per query tile, head and batch entry on the x axis of the grid
+    if (static_cast<uint64_t>((L + 127) / 128) * (F / H) * B > 0x7FFFFFFFull) return FA_B200_ERR_SHAPE;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(y);
     if (all & 15u) return FA_B200_ERR_ALIGNMENT;
     if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return FA_B200_ERR_ALIGNMENT;
     const uint32_t known = FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_SYNC |
-                           FA_B200_FLAG_NO_OVERLAP;
+                           FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT;
     if (flags & ~known) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && (mask || H < 64)) return FA_B200_ERR_FLAGS;
@@ -178,7 +198,7 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
         if (e != cudaSuccess) return static_cast<int>(e);
         c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
-    const dim3 grid((p.L + fa::kTile - 1) / fa::kTile, p.F / H, p.B);
+    const dim3 grid(p.n_q_tiles * p.R * p.B, 1, 1);
     const cudaError_t e = launch_kernel(kern, grid, 128, smem, st, overlap, mq, mk, mv, p);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
@@ -230,7 +250,9 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.B = B;
                 p.L = L;
                 p.F = F;
+                p.launch_id = next_launch_id();
                 p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
+                p.n_q_tiles = p.n_kv_tiles;
                 p.R = F / H;
                 p.q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
                 p.n_items = p.q_pairs * p.R * B;
@@ -269,14 +291,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
     }
     if (rc == FA_B200_OK && (flags & FA_B200_FLAG_SYNC)) {
         e = cudaStreamSynchronize(st);
-        if (e != cudaSuccess) {
-            rc = static_cast<int>(e);
-        } else {
-            uint32_t w[2] = {0, 0};
-            e = cudaMemcpy(w, c->status, sizeof(w), cudaMemcpyDeviceToHost);
-            if (e != cudaSuccess) rc = static_cast<int>(e);
-            else if (w[0] != 0) rc = FA_B200_ERR_DEVICE_TIMEOUT;
-        }
+        rc = e != cudaSuccess ? static_cast<int>(e) : fold_status(c->status);
     }
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
@@ -302,8 +317,8 @@ constexpr uint32_t kNoAllocMaxCtas = 16384;
 static __device__ __align__(256) uint32_t g_noalloc_status[2 * kNoAllocMaxCtas];
 
 struct NoAllocCtx {
+    std::mutex mu;                   // set-up and the attribute bits of this device
     bool ready = false;
-    int cc_major = 0;
     uint32_t* status_dev = nullptr;  // device address of g_noalloc_status on this device
     uint32_t attr_done = 0;
 };
@@ -314,10 +329,13 @@ int launch_simple_noalloc(NoAllocCtx& c, int slot, const CUtensorMap& mq, const 
                           const CUtensorMap& mv, const Params& p, dim3 grid, cudaStream_t st) {
     constexpr int smem = 3 * fa::TileGeom<H>::kTileBytes + 1024;
     auto kern = fa::fa_fwd_simple<H, M, true>;
-    if (!(c.attr_done & (1u << slot))) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        c.attr_done |= (1u << slot);
+    {
+        std::lock_guard<std::mutex> lk(c.mu);
+        if (!(c.attr_done & (1u << slot))) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            c.attr_done |= (1u << slot);
+        }
     }
     kern<<<grid, 128, smem, st>>>(mq, mk, mv, p);
     return static_cast<int>(cudaGetLastError());
@@ -334,10 +352,11 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
     int rc = validate(q, k, v, mask_or_null, y, B, L, F, head_dim, chunk_hint, flags);
     if (rc != FA_B200_OK) return rc;
     const uint32_t H = head_dim;
-    const dim3 grid((L + fa::kTile - 1) / fa::kTile, F / H, B);
-    const uint64_t ctas = static_cast<uint64_t>(grid.x) * grid.y * grid.z;
+    const uint32_t n_q_tiles = (L + fa::kTile - 1) / fa::kTile;
+    const uint64_t ctas = static_cast<uint64_t>(n_q_tiles) * (F / H) * B;
     if (ctas > kNoAllocMaxCtas) return FA_B200_ERR_TOO_LARGE;
     if (device < 0 || device >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+    const dim3 grid(static_cast<uint32_t>(ctas), 1, 1);
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 
     int prev = -1;
@@ -346,23 +365,32 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
     if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
     NoAllocCtx& c = g_noalloc[device];
     {
-        std::lock_guard<std::mutex> lk(g_mu);
+        // Set-up, once per device, with that device current: the compute capability is checked first
+        // (the scratch array only exists in the sm_100a image), then the device address of the
+        // file-scope scratch is looked up.  No allocation.  Calls on other devices do not wait here.
+        std::lock_guard<std::mutex> lk(c.mu);
         if (!c.ready) {
-            // Set-up, once per device, with that device current: compute capability, the device
-            // address of the file-scope scratch, the driver's tensor-map encoder.  No allocation.
             int major = 0;
             e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
-            void* sym = nullptr;
-            if (e == cudaSuccess) e = cudaGetSymbolAddress(&sym, g_noalloc_status);
             if (e != cudaSuccess) {
                 rc = static_cast<int>(e);
+            } else if (major != 10) {
+                rc = FA_B200_ERR_ARCH;
             } else {
-                c.cc_major = major;
-                c.status_dev = static_cast<uint32_t*>(sym);
-                c.ready = true;
+                void* sym = nullptr;
+                e = cudaGetSymbolAddress(&sym, g_noalloc_status);
+                if (e != cudaSuccess) {
+                    rc = static_cast<int>(e);
+                } else {
+                    c.status_dev = static_cast<uint32_t*>(sym);
+                    c.ready = true;
+                }
             }
         }
-        if (rc == FA_B200_OK && g_encode == nullptr) {
+    }
+    if (rc == FA_B200_OK) {
+        std::lock_guard<std::mutex> lk(g_mu);   // the driver's tensor-map encoder is looked up once per process
+        if (g_encode == nullptr) {
             void* fn = nullptr;
             cudaDriverEntryPointQueryResult qres;
             e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -373,49 +401,50 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
         }
-        if (rc == FA_B200_OK && c.cc_major != 10) rc = FA_B200_ERR_ARCH;
-        CUtensorMap mq, mk, mv;
-        if (rc == FA_B200_OK) rc = make_map(&mq, q, B, L, F, H);
-        if (rc == FA_B200_OK) rc = make_map(&mk, k, B, L, F, H);
-        if (rc == FA_B200_OK) rc = make_map(&mv, v, B, L, F, H);
-        if (rc == FA_B200_OK) {
-            // The array keeps what the previous call left: zero the pairs this grid will use, in
-            // stream order ahead of the kernel.
-            e = cudaMemsetAsync(c.status_dev, 0, static_cast<size_t>(ctas) * 2 * sizeof(uint32_t), st);
-            if (e != cudaSuccess) rc = static_cast<int>(e);
-        }
-        if (rc == FA_B200_OK) {
-            Params p;
-            p.y = static_cast<__half*>(y);
-            p.mask = static_cast<const __half*>(mask_or_null);
-            p.status = c.status_dev;   // the address from cudaGetSymbolAddress, never the symbol itself
-            p.B = B;
-            p.L = L;
-            p.F = F;
-            p.n_kv_tiles = (L + fa::kTile - 1) / fa::kTile;
-            p.R = F / H;
-            p.q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
-            p.n_items = p.q_pairs * p.R * B;
-            p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
-            p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+    }
+    CUtensorMap mq, mk, mv;
+    if (rc == FA_B200_OK) rc = make_map(&mq, q, B, L, F, H);
+    if (rc == FA_B200_OK) rc = make_map(&mk, k, B, L, F, H);
+    if (rc == FA_B200_OK) rc = make_map(&mv, v, B, L, F, H);
+    if (rc == FA_B200_OK) {
+        // The array keeps what the previous call left: zero the pairs this grid will use, in
+        // stream order ahead of the kernel.
+        e = cudaMemsetAsync(c.status_dev, 0, static_cast<size_t>(ctas) * 2 * sizeof(uint32_t), st);
+        if (e != cudaSuccess) rc = static_cast<int>(e);
+    }
+    if (rc == FA_B200_OK) {
+        Params p;
+        p.y = static_cast<__half*>(y);
+        p.mask = static_cast<const __half*>(mask_or_null);
+        p.status = c.status_dev;   // the address from cudaGetSymbolAddress, never the symbol itself
+        p.launch_id = 0;           // per-CTA status pairs: no launch word
+        p.B = B;
+        p.L = L;
+        p.F = F;
+        p.n_kv_tiles = n_q_tiles;
+        p.n_q_tiles = n_q_tiles;
+        p.R = F / H;
+        p.q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
+        p.n_items = p.q_pairs * p.R * B;
+        p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
+        p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
 #if defined(FA_TRACE) || defined(FA_CYCLES)
-            p.trace = nullptr;
-            p.trace_cta = 0;
+        p.trace = nullptr;
+        p.trace_cta = 0;
 #endif
-            if (mask_or_null) {
-                switch (H) {
-                    case 16: rc = launch_simple_noalloc<16, true>(c, 4, mq, mk, mv, p, grid, st); break;
-                    case 32: rc = launch_simple_noalloc<32, true>(c, 5, mq, mk, mv, p, grid, st); break;
-                    case 64: rc = launch_simple_noalloc<64, true>(c, 6, mq, mk, mv, p, grid, st); break;
-                    default: rc = launch_simple_noalloc<128, true>(c, 7, mq, mk, mv, p, grid, st); break;
-                }
-            } else {
-                switch (H) {
-                    case 16: rc = launch_simple_noalloc<16, false>(c, 0, mq, mk, mv, p, grid, st); break;
-                    case 32: rc = launch_simple_noalloc<32, false>(c, 1, mq, mk, mv, p, grid, st); break;
-                    case 64: rc = launch_simple_noalloc<64, false>(c, 2, mq, mk, mv, p, grid, st); break;
-                    default: rc = launch_simple_noalloc<128, false>(c, 3, mq, mk, mv, p, grid, st); break;
-                }
+        if (mask_or_null) {
+            switch (H) {
+                case 16: rc = launch_simple_noalloc<16, true>(c, 4, mq, mk, mv, p, grid, st); break;
+                case 32: rc = launch_simple_noalloc<32, true>(c, 5, mq, mk, mv, p, grid, st); break;
+                case 64: rc = launch_simple_noalloc<64, true>(c, 6, mq, mk, mv, p, grid, st); break;
+                default: rc = launch_simple_noalloc<128, true>(c, 7, mq, mk, mv, p, grid, st); break;
+            }
+        } else {
+            switch (H) {
+                case 16: rc = launch_simple_noalloc<16, false>(c, 0, mq, mk, mv, p, grid, st); break;
+                case 32: rc = launch_simple_noalloc<32, false>(c, 1, mq, mk, mv, p, grid, st); break;
+                case 64: rc = launch_simple_noalloc<64, false>(c, 2, mq, mk, mv, p, grid, st); break;
+                default: rc = launch_simple_noalloc<128, false>(c, 3, mq, mk, mv, p, grid, st); break;
             }
         }
     }
@@ -567,12 +596,7 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
         if (rc == FA_B200_OK && e1 != cudaSuccess) rc = static_cast<int>(e1);
         if (rc == FA_B200_OK && e2 != cudaSuccess) rc = static_cast<int>(e2);
         if (rc == FA_B200_OK && e3 != cudaSuccess) rc = static_cast<int>(e3);
-        if (rc == FA_B200_OK) {
-            uint32_t w[2] = {0, 0};
-            e = cudaMemcpy(w, c->status, sizeof(w), cudaMemcpyDeviceToHost);
-            if (e != cudaSuccess) rc = static_cast<int>(e);
-            else if (w[0] != 0) rc = FA_B200_ERR_DEVICE_TIMEOUT;
-        }
+        if (rc == FA_B200_OK) rc = fold_status(c->status);
     }
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
@@ -585,7 +609,7 @@ const char* fa_b200_strerror(int code) {
         case FA_B200_ERR_HEAD_DIM: return "head_dim must be 16, 32, 64 or 128";
         case FA_B200_ERR_CHUNK:
             return "chunk_size must be a power of two in [16, 128], at most 2*head_dim, and not 16 with head_dim 128";
-        case FA_B200_ERR_SHAPE: return "B, L, F must be positive, F divisible by head_dim, B and F/head_dim at most 65535";
+        case FA_B200_ERR_SHAPE: return "B, L, F must be positive, F divisible by head_dim, and ceil(L/128)*(F/head_dim)*B below 2^31";
         case FA_B200_ERR_ALIGNMENT: return "q, k, v and y must be 16-byte aligned";
         case FA_B200_ERR_ARCH: return "the device is not compute capability 10.x (sm_100a)";
         case FA_B200_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
@@ -625,7 +649,7 @@ int fa_b200_read_status(int device, uint32_t out[2]) {
     if (rc == FA_B200_OK) {
         e = cudaDeviceSynchronize();
         if (e == cudaSuccess) e = cudaMemcpy(out, c->status, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
-        if (e == cudaSuccess) e = cudaMemset(c->status, 0, 2 * sizeof(uint32_t));
+        if (e == cudaSuccess) e = cudaMemset(c->status, 0, kStatusWords * sizeof(uint32_t));
         if (e != cudaSuccess) rc = static_cast<int>(e);
     }
     if (prev != device) (void)cudaSetDevice(prev);
@@ -669,7 +693,14 @@ int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
     alignas(16) static const char d[16] = {0};
     const int rc = validate(d, d, d, has_mask ? d : nullptr, d, B, L, F, head_dim, 0, flags);
     if (rc != FA_B200_OK) return rc;
-    return select_kernel(B, L, F, head_dim, has_mask != 0, flags, 148);
+    // the SM count of the current device decides, as it does in a launch; 148 (B200) without a device
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        (void)cudaGetLastError();
+        sms = 148;
+    }
+    return select_kernel(B, L, F, head_dim, has_mask != 0, flags, sms);
 }
 
 }  // extern "C"

@@ -35,7 +35,9 @@ namespace fa {
 struct Params {
     __half* y;            // [B, L, F]
     const __half* mask;   // [B, L, L] or nullptr
-    uint32_t* status;     // device status word pair, see WaitCtl
+    uint32_t* status;     // device status block {code, count, launch id, -}, see WaitCtl
+    uint32_t launch_id;   // non-zero and different for every launch of the process
+    uint32_t n_q_tiles;   // ceil(L / 128)
     uint32_t B, L, F;
     uint32_t n_kv_tiles;  // ceil(L / 128)
     uint32_t R;           // heads = F / H
@@ -297,17 +299,49 @@ __device__ __forceinline__ void mask_tail(float (&s)[kTile], int valid) {
         if (i >= valid) s[i] = -INFINITY;
 }
 
+// s[i] += mask[i] * to_score for the first `valid` keys of a tile.  With `vec` (the row starts on a
+// 16-byte boundary: L a multiple of 8) whole groups of eight mask values are read with one 16-byte
+// load; the ragged remainder and unaligned rows are read value by value.
+__device__ __forceinline__ void add_mask_row(float (&s)[kTile], const __half* mrow, int valid, float to_score,
+                                             bool vec) {
+    if (vec) {
+#pragma unroll
+        for (int i0 = 0; i0 < kTile; i0 += 8) {
+            if (i0 + 8 <= valid) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(mrow + i0));
+                const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[e]));
+                    s[i0 + 2 * e] = fmaf(f.x, to_score, s[i0 + 2 * e]);
+                    s[i0 + 2 * e + 1] = fmaf(f.y, to_score, s[i0 + 2 * e + 1]);
+                }
+            } else {
+#pragma unroll
+                for (int i = i0; i < i0 + 8; ++i)
+                    if (i < valid) s[i] = fmaf(__half2float(mrow[i]), to_score, s[i]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kTile; ++i)
+            if (i < valid) s[i] = fmaf(__half2float(mrow[i]), to_score, s[i]);
+    }
+}
+
 // ============================================================================ simple kernel
-// grid = (ceil(L/128), R, B), block = 128.  Thread t owns query row t of the tile (TMEM lane t).
+// grid = ceil(L/128) * R * B CTAs on the x axis (query tile fastest, then head, then batch; one axis
+// so that none of the three is held to the 65535 of the y and z axes), block = 128.  Thread t owns
+// query row t of the tile (TMEM lane t).
 // kPerCtaStatus (only the no-allocation entry point sets it): p.status is an array of one status
-// pair per CTA instead of one pair per device, so no atomics from different CTAs meet.
+// pair per CTA instead of one block per device, so no atomics from different CTAs meet.
 template <int H, bool kHasMask, bool kPerCtaStatus = false>
 __global__ void __launch_bounds__(128)
 fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const Params p) {
     using G = TileGeom<H>;
     constexpr uint32_t kTmemCols = 256;  // S/P in [0,128), O in [128, 128+H)
-    enum { BAR_Q = 0, BAR_K, BAR_V, BAR_S, BAR_O, BAR_COUNT };
+    enum { BAR_Q = 0, BAR_K, BAR_V, BAR_S, BAR_O, BAR_DRAIN, BAR_COUNT };
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[BAR_COUNT];
@@ -316,7 +350,8 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5;
-    const uint32_t q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+    const uint32_t q_tile = blockIdx.x % p.n_q_tiles;
+    const uint32_t head = (blockIdx.x / p.n_q_tiles) % p.R, batch = blockIdx.x / (p.n_q_tiles * p.R);
     const int32_t col0 = static_cast<int32_t>(head * H);
     const int32_t q_row0 = static_cast<int32_t>(q_tile * kTile);
 
@@ -324,10 +359,8 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t sQ = smem_base, sK = sQ + G::kTileBytes, sV = sK + G::kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    const WaitCtl ctl{kPerCtaStatus
-                          ? p.status + 2u * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z))
-                          : p.status,
-                      &abort_flag, kWaitCapCycles};
+    const WaitCtl ctl{kPerCtaStatus ? p.status + 2u * blockIdx.x : p.status, &abort_flag, kWaitCapCycles,
+                      kPerCtaStatus ? nullptr : p.status + 2, p.launch_id};
 
     if (tid == 0) {
 #pragma unroll
@@ -349,16 +382,22 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     // written: the kernel before this one in the stream must have completed.
     grid_dep_wait();
     grid_dep_launch();
+    if (tid == 96) leave_early_if_launch_failed(ctl);
     const uint32_t tmem_base = tmem_slot;
     const uint32_t lane_off = (warp * 32u) << 16;
     const uint32_t tS = tmem_base + lane_off;          // this thread's score row
     const uint32_t tO = tmem_base + lane_off + 128u;   // this thread's output row
     const uint32_t n_tiles = p.n_kv_tiles;
 
+    // Thread 0 starts every TMA copy and issues every MMA.  Once a wait of this CTA has given up it
+    // starts nothing new (`live`), so that at the end at most one copy per barrier is in flight.
+    uint32_t nk = 0, nv = 0;   // K and V tiles requested so far (thread 0)
+    bool live = true;
     if (tid == 0) {
         load_tile<H>(sQ, &tmQ, bar(BAR_Q), col0, q_row0, batch);
         load_tile<H>(sK, &tmK, bar(BAR_K), col0, 0, batch);
         load_tile<H>(sV, &tmV, bar(BAR_V), col0, 0, batch);
+        nk = nv = 1;
     }
 
     float m = -INFINITY, l = 0.f;
@@ -368,17 +407,21 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t ph = j & 1u;
         if (tid == 0) {
-            if (j == 0) mbar_wait(bar(BAR_Q), 0, ctl, kRoleSimple | BAR_Q);
-            mbar_wait(bar(BAR_K), ph, ctl, kRoleSimple | BAR_K);
+            if (j == 0) live &= mbar_wait(bar(BAR_Q), 0, ctl, kRoleSimple | BAR_Q);
+            live &= mbar_wait(bar(BAR_K), ph, ctl, kRoleSimple | BAR_K);
             tc_fence_after();
-            issue_qk<H>(tmem_base, sQ, sK);
-            tc_commit(bar(BAR_S));
+            if (live) {
+                issue_qk<H>(tmem_base, sQ, sK);
+                tc_commit(bar(BAR_S));
+            }
         }
-        mbar_wait(bar(BAR_S), ph, ctl, kRoleSimple | BAR_S);
+        const bool s_ok = mbar_wait(bar(BAR_S), ph, ctl, kRoleSimple | BAR_S);
         tc_fence_after();
         // The K tile is free again: fetch the next one while the softmax runs.
-        if (tid == 0 && j + 1 < n_tiles)
+        if (tid == 0 && j + 1 < n_tiles && (live &= s_ok)) {
             load_tile<H>(sK, &tmK, bar(BAR_K), col0, static_cast<int32_t>((j + 1) * kTile), batch);
+            ++nk;
+        }
 
         float s[kTile];
         __syncwarp();
@@ -389,9 +432,8 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const __half* mrow = p.mask + (static_cast<size_t>(batch) * p.L + q_row) * p.L +
                                      static_cast<size_t>(j) * kTile;
                 const int valid = min(static_cast<int>(p.L - j * kTile), kTile);
-#pragma unroll
-                for (int i = 0; i < kTile; ++i)
-                    if (i < valid) s[i] = fmaf(__half2float(mrow[i]), p.mask_to_score, s[i]);
+                add_mask_row(s, mrow, valid, p.mask_to_score,
+                             ((p.L & 7u) | (reinterpret_cast<uintptr_t>(p.mask) & 15u)) == 0u);
             }
         }
         if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
@@ -404,21 +446,38 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         __syncthreads();
         if (tid == 0) {
             tc_fence_after();
-            mbar_wait(bar(BAR_V), ph, ctl, kRoleSimple | BAR_V);
-            issue_pv<H>(tmem_base + 128u, tmem_base, sV, j > 0 ? 1u : 0u);
-            tc_commit(bar(BAR_O));
+            live &= mbar_wait(bar(BAR_V), ph, ctl, kRoleSimple | BAR_V);
+            if (live) {
+                issue_pv<H>(tmem_base + 128u, tmem_base, sV, j > 0 ? 1u : 0u);
+                tc_commit(bar(BAR_O));
+            }
         }
-        mbar_wait(bar(BAR_O), ph, ctl, kRoleSimple | BAR_O);
+        const bool o_ok = mbar_wait(bar(BAR_O), ph, ctl, kRoleSimple | BAR_O);
         tc_fence_after();
         __syncwarp();
-        if (tid == 0 && j + 1 < n_tiles)
+        if (tid == 0 && j + 1 < n_tiles && (live &= o_ok)) {
             load_tile<H>(sV, &tmV, bar(BAR_V), col0, static_cast<int32_t>((j + 1) * kTile), batch);
+            ++nv;
+        }
     }
 
     // Y = O / l
     {
         __half* dst = p.y + (static_cast<size_t>(batch) * p.L + q_row) * p.F + head * H;
         store_o_row<H>(tO, 1.f / l, dst, row_valid);
+    }
+    if (tid == 0 && abort_flag != 0u) {
+        // A wait gave up, so the waits behind it returned at once and MMAs this thread issued may
+        // still be running.  They retire whatever happened to their inputs; tensor memory and the
+        // shared-memory tiles they use are not released before they have.  Likewise the TMA copies
+        // this thread started: each of Q, K, V has at most one in flight, the last one requested.
+        tc_commit(bar(BAR_DRAIN));
+        mbar_wait_certain(bar(BAR_DRAIN), 0, ctl, kRoleDrain | BAR_DRAIN);
+        const long long t0 = clock64();
+        while (!(mbar_try_wait(bar(BAR_Q), 0) && mbar_try_wait(bar(BAR_K), (nk - 1u) & 1u) &&
+                 mbar_try_wait(bar(BAR_V), (nv - 1u) & 1u)) &&
+               clock64() - t0 < 200000000LL) {
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -527,7 +586,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t sStage = sRing + C::kRingBytes;   // epilogue staging, 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles};
+    const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles, p.status + 2, p.launch_id};
 
     if (tid == 0) {
         prefetch_tensormap(&tmY);
@@ -559,6 +618,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // stop at this same point: the overlap is never deeper than one launch).
     grid_dep_wait();
     grid_dep_launch();
+    if (tid == 15 * 32) leave_early_if_launch_failed(ctl);   // warp 15 has no other work
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
 #if defined(FA_TRACE) || defined(FA_CYCLES)
     if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512] = static_cast<unsigned long long>(clock64());
@@ -740,8 +800,14 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint32_t tO0 = tmem_base + C::kColO0, tO1 = tmem_base + C::kColO1;
             const uint32_t tP0 = tmem_base + C::kColP0, tP1 = tmem_base + C::kColP1;
             auto slot_addr = [&](uint32_t t) { return sRing + (t % NS) * G::kTileBytes; };
+            // Once one of this warp's waits has given up (`ok` false) it issues nothing more: what it
+            // would multiply has not arrived.
+            bool ok = true;
+            auto mwait = [&](uint32_t b, uint32_t parity, const WaitCtl& wc, uint32_t code) {
+                ok &= mbar_wait(b, parity, wc, code);
+            };
             auto wait_full = [&](uint32_t t) {
-                mbar_wait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
+                mwait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
             };
             auto free_slot = [&](uint32_t t) { tc_commit(bar(BAR_EMPTY + (t % NS))); };
 #ifdef FA_TRACE
@@ -753,19 +819,19 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // ring item 2g is the K tile of global step g, item 2g+1 its V tile
             if (steps > 0 && warp == 12) {
                 // S tiles of the very first step
-                mbar_wait(bar(BAR_QFULL0), 0, ctl, kRoleMma | BAR_QFULL0);
+                mwait(bar(BAR_QFULL0), 0, ctl, kRoleMma | BAR_QFULL0);
                 wait_full(0);
                 tc_fence_after();
-                if (leader) {
+                if (leader && ok) {
                     issue_qk<H>(tS0, sQ, slot_addr(0));
                     tc_commit(bar(BAR_S0));
                     if (n == 1) tc_commit(bar(BAR_QEMPTY0));
                 }
-                mbar_wait(bar(BAR_QFULL1), 0, ctl, kRoleMma | BAR_QFULL1);
+                mwait(bar(BAR_QFULL1), 0, ctl, kRoleMma | BAR_QFULL1);
                 // one S buffer for both tiles: tile 0's scores must have been read first
-                if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 0, ctl, kRoleMma | BAR_SFREE0);
+                if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0, ctl, kRoleMma | BAR_SFREE0);
                 tc_fence_after();
-                if (leader) {
+                if (leader && ok) {
                     issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
                     tc_commit(bar(BAR_S1));
                     if (n == 1) tc_commit(bar(BAR_QEMPTY1));
@@ -785,24 +851,24 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const uint32_t tk = 2 * g + 2;
                         const bool next_new_item = j + 1 == n;    // step g + 1 opens item k + 1
                         if (!(polled && mbar_poll_end<0>())) wait_full(tk);
-                        if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                        if (next_new_item) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
                         // With one S buffer its uses are numbered 2g + i (tile i, step g) and use u
                         // needs the reading of use u - 1 (one barrier, phase = use); with one buffer
                         // per tile the reading of step g of that tile.
-                        if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 1u, ctl, kRoleMma | BAR_SFREE0);
-                        else mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                        if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 1u, ctl, kRoleMma | BAR_SFREE0);
+                        else mwait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
                         FA_TRACE_EV(0, 11);  // S0 read by the softmax warps
                         tc_fence_after();
-                        if (leader) {
+                        if (leader && ok) {
                             issue_qk<H>(tS0, sQ, slot_addr(tk));
                             tc_commit(bar(BAR_S0));
                             // the Q K^T of an item's last key step is its last use of the query tile
                             if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
                         }
                         FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
-                        if (next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                        if constexpr (C::kSharedS) mbar_wait(bar(BAR_SFREE0), 0u, ctl, kRoleMma | BAR_SFREE0);
-                        else mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        if (next_new_item) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                        if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0u, ctl, kRoleMma | BAR_SFREE0);
+                        else mwait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
                         FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
                         tc_fence_after();
                         polled = g + 2 < steps;
@@ -810,7 +876,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             const uint32_t nk = tk + 2;
                             mbar_poll_begin<0>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
                         }
-                        if (leader) {
+                        if (leader && ok) {
                             issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                             tc_commit(bar(BAR_S1));
                             if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
@@ -825,17 +891,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const uint32_t tv = 2 * g + 1;
                         const uint32_t acc = j > 0 ? 1u : 0u;
                         if (!(polled && mbar_poll_end<1>())) wait_full(tv);
-                        if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
-                        mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                        mwait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
                         FA_TRACE_EV(3, 2);   // P0 ready
                         tc_fence_after();
-                        if (leader) {
+                        if (leader && ok) {
                             issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
                             tc_commit(bar(BAR_PV0));
                         }
                         FA_TRACE_EV(3, 8);   // P V of tile 0 issued
-                        if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
-                        mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                        mwait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
                         FA_TRACE_EV(3, 5);   // P1 ready
                         tc_fence_after();
                         polled = g + 1 < steps;
@@ -843,7 +909,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             const uint32_t nv = tv + 2;
                             mbar_poll_begin<1>(bar(BAR_FULL + (nv % NS)), (nv / NS) & 1u);
                         }
-                        if (leader) {
+                        if (leader && ok) {
                             issue_pv<H>(tO1, tP1, slot_addr(tv), acc);
                             tc_commit(bar(BAR_PV1));
                             free_slot(tv);
@@ -875,16 +941,16 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         if (!ok_v) wait_full(tv);
                         if (more) {
                             if (!ok_k) wait_full(tk);
-                            if (next_new_item) mbar_wait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
-                            if (!ok_s0) mbar_wait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                            if (next_new_item) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
+                            if (!ok_s0) mwait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
                         }
                     }
-                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
+                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
                     FA_TRACE_EV(0, 1);   // V and next K landed, S0 read by the softmax warps
                     // tile 0
                     if (more) {
                         tc_fence_after();
-                        if (leader) {
+                        if (leader && ok) {
                             issue_qk<H>(tS0, sQ, slot_addr(tk));
                             tc_commit(bar(BAR_S0));
                             // the Q K^T of an item's last key step is its last use of the query tile
@@ -892,23 +958,23 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                     FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
-                    mbar_wait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
+                    mwait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
                     FA_TRACE_EV(0, 2);   // P0 ready
                     tc_fence_after();
                     if (more) mbar_poll_begin<3>(bar(BAR_SFREE1), g & 1u);   // read behind the P V below
-                    if (leader) {
+                    if (leader && ok) {
                         issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
                         tc_commit(bar(BAR_PV0));
                     }
                     FA_TRACE_EV(0, 8);   // P V of tile 0 issued
                     // tile 1
-                    if (more && next_new_item) mbar_wait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                    if (j == 0 && k > 0) mbar_wait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                    if (more && next_new_item) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
+                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
                     if (more) {
-                        if (!mbar_poll_end<3>()) mbar_wait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
+                        if (!mbar_poll_end<3>()) mwait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
                         FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
                         tc_fence_after();
-                        if (leader) {
+                        if (leader && ok) {
                             issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                             tc_commit(bar(BAR_S1));
                             if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
@@ -916,7 +982,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                     FA_TRACE_EV(0, 7);   // next Q K^T of tile 1 issued
-                    mbar_wait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
+                    mwait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
                     FA_TRACE_EV(0, 5);   // P1 ready
                     tc_fence_after();
                     // what the next step starts with: test now, read at the top of the next step
@@ -927,7 +993,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         mbar_poll_begin<1>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
                         mbar_poll_begin<2>(bar(BAR_SFREE0), (g + 1u) & 1u);
                     }
-                    if (leader) {
+                    if (leader && ok) {
                         issue_pv<H>(tO1, tP1, slot_addr(tv), acc);
                         tc_commit(bar(BAR_PV1));
                         free_slot(tv);
@@ -937,9 +1003,11 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
             const int bar_final = warp == 12 ? BAR_FINAL : BAR_FINAL2;
+            // Every MMA this warp issued has to retire before the CTA releases tensor memory and shared
+            // memory, whether or not a wait gave up on the way: this wait does not look at the abort flag.
             if (leader) tc_commit(bar(bar_final));
             __syncwarp();
-            mbar_wait(bar(bar_final), 0, ctl, kRoleMma | static_cast<uint32_t>(bar_final));
+            mbar_wait_certain(bar(bar_final), 0, ctl, kRoleMma | static_cast<uint32_t>(bar_final));
         } else if (warp == 13 && elect_one()) {
             // -------------------------------------------------------------- TMA producer
             uint32_t t = 0;           // ring item

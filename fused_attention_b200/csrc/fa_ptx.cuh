@@ -86,15 +86,34 @@ __device__ __forceinline__ uint32_t mbar_poll_end() {
     return ok;
 }
 
-// Where a bounded wait reports: a device status word pair and a CTA-wide abort flag.
+// Where a bounded wait reports: a device status block and a CTA-wide abort flag.
 struct WaitCtl {
     uint32_t* status;              // global: [0] first failure code, [1] number of reporting CTAs
     volatile uint32_t* abort_flag; // shared: non-zero once any wait of this CTA has expired
     long long cap_cycles;          // how long one wait may spin
+    uint32_t* launch_word;         // global, may be null: receives launch_id when a wait expires, so that
+    uint32_t launch_id;            // CTAs of the same launch that start later leave at once
 };
 
 // About two seconds at 2 GHz; a whole launch of the largest supported problem takes milliseconds.
 constexpr long long kWaitCapCycles = 4000000000LL;
+
+__device__ __forceinline__ void wait_expired(const WaitCtl& ctl, uint32_t code) {
+    if (atomicExch(const_cast<uint32_t*>(ctl.abort_flag), 1u) == 0u) {
+        atomicCAS(ctl.status, 0u, code);
+        atomicAdd(ctl.status + 1, 1u);
+        if (ctl.launch_word != nullptr) atomicExch(ctl.launch_word, ctl.launch_id);
+    }
+}
+
+// A CTA that starts after another CTA of its own launch has given up does not wait for anything:
+// it sets its abort flag, runs through its loops and leaves (one thread calls this, no barrier needed:
+// the flag is only read on the slow path of a wait).
+__device__ __forceinline__ void leave_early_if_launch_failed(const WaitCtl& ctl) {
+    if (ctl.launch_word != nullptr &&
+        *reinterpret_cast<volatile uint32_t*>(ctl.launch_word) == ctl.launch_id)
+        *ctl.abort_flag = 1u;
+}
 
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtl ctl,
                                             uint32_t code) {
@@ -104,10 +123,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Wa
         if ((++spins & 63u) == 0u) {
             if (*ctl.abort_flag != 0u) return false;
             if (clock64() - t0 > ctl.cap_cycles) {
-                if (atomicExch(const_cast<uint32_t*>(ctl.abort_flag), 1u) == 0u) {
-                    atomicCAS(ctl.status, 0u, code);
-                    atomicAdd(ctl.status + 1, 1u);
-                }
+                wait_expired(ctl, code);
                 return false;
             }
         }
@@ -124,10 +140,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
         __nanosleep(sleep_ns);
         if (*ctl.abort_flag != 0u) return false;
         if (clock64() - t0 > ctl.cap_cycles) {
-            if (atomicExch(const_cast<uint32_t*>(ctl.abort_flag), 1u) == 0u) {
-                atomicCAS(ctl.status, 0u, code);
-                atomicAdd(ctl.status + 1, 1u);
-            }
+            wait_expired(ctl, code);
             return false;
         }
     }
@@ -142,6 +155,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl
                                           uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, ctl, code);
+}
+
+// Wait for a completion that is certain to come, such as the retirement of MMAs that have been
+// issued (tcgen05.commit): it does NOT return early when the CTA's abort flag is set, because the
+// caller is about to release what those operations still use (tensor memory, shared memory).  It
+// has the same cap as every other wait.
+__device__ __forceinline__ bool mbar_wait_certain(uint32_t bar, uint32_t parity, WaitCtl ctl,
+                                                  uint32_t code) {
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u && clock64() - t0 > ctl.cap_cycles) {
+            wait_expired(ctl, code);
+            return false;
+        }
+    }
+    return true;
 }
 
 // ----------------------------------------------------------------------------- launch overlap

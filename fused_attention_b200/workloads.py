@@ -1,6 +1,7 @@
 """The named workloads (shapes and value distributions) and the seeded synthetic input generator.
 
-The shapes are the five configurations the benchmark specification lists; no dataset is involved:
+The shapes are the five configurations the benchmark specification lists, plus the two of the
+reference's own benchmark script; no dataset is involved:
 entries are i.i.d. Gaussian, drawn on the CPU in fp32 from a seeded ``torch.Generator``, scaled by
 sigma and rounded to fp16, in the operator's ``[B, L, R*H]`` layout.  The reference's own tests
 draw N(0,1) inputs with seed 179 (``tests/test_fused_attn.py:13-25``); seeds here are 179 + index.
@@ -41,8 +42,14 @@ WORKLOADS = {
     "vit_l16_ragged": Workload("vit_l16_ragged", 64, 16, 197, 64, 1.0, 181),
     "llama7b_prefill": Workload("llama7b_prefill", 4, 32, 2048, 128, 0.5, 182),
     "long_context": Workload("long_context", 1, 32, 16384, 128, 1.0, 183),
+    # the shape of the reference's own benchmark script (tests/benchmark_fused_attn.py:9-22; README.md:110-127):
+    # L=2048, F=5120, H=128 (R=40), N(0,1) inputs, batch 4 and 16
+    "ref_readme_b4": Workload("ref_readme_b4", 4, 40, 2048, 128, 1.0, 184),
+    "ref_readme_b16": Workload("ref_readme_b16", 16, 40, 2048, 128, 1.0, 185),
 }
 HEADLINE = "llama7b_prefill"
+# the five configurations of the benchmark specification, in its order
+BENCH_WORKLOADS = ("tiny", "bert_base", "vit_l16_ragged", "llama7b_prefill", "long_context")
 
 
 def make_inputs(B: int, L: int, F: int, sigma: float = 1.0, seed: int = 179, pin: bool = False):

@@ -5,7 +5,8 @@
  * fp32 accumulation and fp32 online-softmax state, no L x L score matrix in global memory.
  *
  * Tensor contract (same as the reference operator, src/fused_attn_extention.cu:24-70):
- * q, k, v, y are contiguous fp16 device arrays of logical shape [B, L, F] with F = R * head_dim;
+ * q, k, v, y are contiguous fp16 device arrays of logical shape [B, L, F] with F = R * head_dim
+ * (any B, R, L with ceil(L/128) * R * B below 2^31);
  * head h owns columns [h*head_dim, (h+1)*head_dim) of the last axis
  * (include/fused_attn.cuh:681-696 in the reference).  The optional mask is a contiguous fp16
  * array [B, L, L] that is ADDED to the scaled scores of every head (reference
@@ -45,13 +46,23 @@ enum {
     FA_B200_FLAG_FORCE_SIMPLE = 1u,    /* always use the one-tile-per-CTA kernel                */
     FA_B200_FLAG_FORCE_PIPELINED = 2u, /* always use the warp-specialised kernel (H in {64,128}) */
     FA_B200_FLAG_SYNC = 4u,            /* synchronise the stream before returning and fold the
-                                          device status word into the return value             */
-    FA_B200_FLAG_NO_OVERLAP = 8u       /* plain launch.  By default the kernel is launched with the
+                                          device status word into the return value; a report is
+                                          cleared when it is returned (see fa_b200_read_status) */
+    FA_B200_FLAG_NO_OVERLAP = 8u,      /* plain launch.  By default the kernel is launched with the
                                           programmatic-stream-serialization attribute: its CTAs may
                                           become resident and set up their barriers and tensor memory
                                           while the previous kernel of the stream drains; they touch
                                           global memory only once that kernel has completed, so the
                                           stream's ordering guarantees are unchanged             */
+    FA_B200_FLAG_NO_SPLIT = 16u        /* never divide the key axis of one (batch, head, query rows)
+                                          problem among several CTAs.  By default the warp-specialised
+                                          kernel may do so to keep every SM busy when the work items
+                                          do not fill a whole number of rounds; the partial results
+                                          are merged in fp32, in a fixed order, so a call repeats bit
+                                          for bit, but where the cuts fall depends on how many
+                                          (batch, head) pairs the call holds.  With this flag the bits
+                                          of one (batch, head) do not depend on what else is in the
+                                          call (a shard reproduces the undivided job exactly)       */
 };
 
 /*
@@ -94,12 +105,12 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v,
  * The same operator for callers that must not allocate.  It has no counterpart in the reference
  * (whose binding always allocates its output and whose launcher has no workspace at all).
  *
- * Who needs it: code that runs where cudaMalloc is off limits or unwanted: inside a region that a
- * framework is recording for later replay, in a process whose device memory is entirely owned by
- * another allocator or already handed out, in a latency-critical loop where an allocation would
- * synchronise the device.  fa_b200_attention_forward allocates (once per device) a small status
- * buffer for its kernels; this entry point never calls cudaMalloc, cudaFree or any allocating
- * library routine.
+ * Who needs it: code that runs where cudaMalloc is off limits or unwanted: a process whose device
+ * memory is entirely owned by another allocator or already handed out (an inference server that
+ * reserves the whole GPU at start-up), a plugin that may not grow its host's footprint, a
+ * latency-critical loop where an allocation would synchronise the device.
+ * fa_b200_attention_forward allocates (once per device) a small status buffer for its kernels;
+ * this entry point never calls cudaMalloc, cudaFree or any allocating library routine.
  *
  * How: it always runs the one-tile-per-CTA kernel, and that kernel's only scratch (a pair of
  * status words per CTA, written when a bounded device-side wait expires) lives in a fixed array
@@ -111,7 +122,8 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v,
  *     stream order, ahead of its kernel) and the array otherwise keeps what the last call left;
  *     two calls whose kernels overlap on the GPU (different streams) race on it, so serialise them;
  *   - the first call on a device looks up the array's device address and sets the kernel's
- *     shared-memory attribute; make that first call outside any stream capture.
+ *     shared-memory attribute; make that first call before any stream capture begins.  Calls on
+ *     different devices do not wait for one another.
  * flags: 0 or FA_B200_FLAG_SYNC (synchronise the stream and return FA_B200_ERR_DEVICE_TIMEOUT if
  * any CTA reported).  Inputs, outputs, head_dim, chunk_hint, mask: as fa_b200_attention_forward.
  */
@@ -139,6 +151,11 @@ int fa_b200_query(int device, int32_t out[4]);
  * Read and clear the per-device status word written by kernels whose bounded waits expired:
  * out[0] = first failure code (0 = none; bits 8.. = role, bits 0..7 = barrier id),
  * out[1] = number of CTAs that reported.  Synchronises the device.
+ * The word is shared by every launch on the device and stays set until it is read here, or
+ * returned by a call with FA_B200_FLAG_SYNC or by fa_b200_attention_forward_host (both clear it
+ * when they return FA_B200_ERR_DEVICE_TIMEOUT).  An asynchronous call never looks at it: after a
+ * launch whose wait expired its output is garbage and only this word says so.  Once one CTA of a
+ * launch has given up, the CTAs of that launch that start later leave at once.
  * No counterpart in the reference (it has no device-side error reporting).
  */
 int fa_b200_read_status(int device, uint32_t out[2]);

@@ -2,6 +2,9 @@
 
   python oracle/build_ref.py [/path/to/reference]
 
+Without an argument the checkout is looked for in $FA_REFERENCE_ROOT, then in a directory named
+`reference` beside this repository.
+
 The reference is header-only (include/fused_attn.cuh); nvcc compiles oracle/ref_wmma_wrapper.cu
 against that header in place.  Nothing is copied from the reference; the output directory is
 git-ignored.  Returns quietly when the reference checkout is absent.
@@ -18,7 +21,15 @@ OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libref_fused_attn.so")
 
 
-def build(ref_root: str = "/root/reference", force: bool = False) -> str | None:
+def default_ref_root() -> str:
+    env = os.environ.get("FA_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root: str | None = None, force: bool = False) -> str | None:
+    ref_root = ref_root or default_ref_root()
     header = os.path.join(ref_root, "include", "fused_attn.cuh")
     if not os.path.exists(header):
         return OUT if os.path.exists(OUT) else None
@@ -34,4 +45,5 @@ def build(ref_root: str = "/root/reference", force: bool = False) -> str | None:
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(args[0] if args else None, force="--force" in sys.argv))

@@ -45,4 +45,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("FA_REFERENCE_ROOT"):
+        sys.exit("usage: python tests/golden/make_golden.py <reference checkout>   (or set FA_REFERENCE_ROOT)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["FA_REFERENCE_ROOT"])

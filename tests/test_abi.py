@@ -105,6 +105,10 @@ def test_kernel_selection(lib):
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_FORCE_SIMPLE) == 1
     assert sel(1, 256, 256, 64, 0, _lib.FLAG_FORCE_PIPELINED) == 2
     assert sel(1, 256, 250, 64, 0, 0) == _lib.ERR_SHAPE
+    # no limit of 65535 on batch entries or heads (the reference has none on its batch axis)
+    assert sel(70000, 64, 64, 64, 0, 0) == 1
+    assert sel(1, 64, 70000 * 16, 16, 0, 0) == 1
+    assert sel(1 << 20, 128 * 2048, 64, 64, 0, 0) == _lib.ERR_SHAPE   # 2^31 CTAs: too many for one grid axis
 
 
 def test_missing_library_is_loud(monkeypatch, tmp_path):

@@ -82,6 +82,43 @@ def test_full_size_configurations_sampled_rows(name):
         assert m["max_abs"] / rms < 2e-2, m
 
 
+def _fp32_attention_on_device(q, k, v, H, b, h):
+    """softmax(q k^T / sqrt(H)) v of one (batch, head) in fp32 on the GPU, in blocks of 2048 query rows."""
+    qf, kf, vf = (t[b, :, h * H:(h + 1) * H].float() for t in (q, k, v))
+    out = torch.empty_like(qf)
+    for r0 in range(0, qf.shape[0], 2048):
+        out[r0:r0 + 2048] = torch.softmax(qf[r0:r0 + 2048] @ kf.T / H ** 0.5, -1) @ vf
+    return out
+
+
+@pytest.mark.parametrize("name", ["llama7b_prefill", "long_context"])
+def test_full_size_configurations_every_row(name):
+    """Every query row of every (batch, head) of the two large configurations, both kernels, against
+    fp32 attention computed on the same GPU (the CPU oracle would need minutes to hours at these sizes);
+    that checker is itself held against the CPU oracle on sampled rows of every head."""
+    w = WORKLOADS[name]
+    hq, hk, hv = workload_inputs(w)
+    q, k, v = hq.cuda(), hk.cuda(), hv.cuda()
+    g = torch.Generator().manual_seed(w.seed + 1)
+    rows = sorted(set(torch.randint(0, w.L, (24,), generator=g).tolist()) | {0, w.L - 1})
+    cpu = oracle(hq, hk, hv, w.H, query_rows=rows)                 # [B, rows, F]
+    ys = {flags: fa.attention_forward(w.H, 128, q, k, v, flags=flags) for flags in (PIPE, SIMPLE)}
+    torch.cuda.synchronize()
+    worst = {PIPE: [0.0, 0.0], SIMPLE: [0.0, 0.0]}
+    checker_worst = 0.0
+    for b in range(w.B):
+        for h in range(w.R):
+            ref = _fp32_attention_on_device(q, k, v, w.H, b, h)
+            checker_worst = max(checker_worst, float((ref[rows].cpu() - cpu[b, :, h * w.H:(h + 1) * w.H]).abs().max()))
+            for flags, y in ys.items():
+                d = (y[b, :, h * w.H:(h + 1) * w.H].float() - ref).abs()
+                worst[flags][0] = max(worst[flags][0], float(d.max()))
+                worst[flags][1] = max(worst[flags][1], float(d.mean()))
+    assert checker_worst <= 2e-5, checker_worst      # fp32 against fp32: only the order of summation differs
+    for flags in (PIPE, SIMPLE):
+        assert worst[flags][0] <= MAX_ABS_TOL and worst[flags][1] <= MEAN_ABS_TOL, (flags, worst[flags])
+
+
 @pytest.mark.parametrize("H", [16, 32, 64, 128])
 @pytest.mark.parametrize("L", [1, 2, 31, 127, 128, 129, 255, 256, 257, 383, 385, 640])
 def test_ragged_lengths(H, L):
@@ -214,9 +251,10 @@ def test_large_logits_stay_finite():
 def test_reference_maximum_moves_between_key_tiles(H, pattern):
     """Scores that jump by far more than 2^8 (in the exp2 domain) from one key tile to the next:
     rising (every tile forces a new reference and an O rescale), falling (the first reference stays,
-    later P underflow to zero) and a single late spike.  The pipelined kernel hands P of a key tile
-    to the MMA warp in two parts (keys 0-95, keys 96-127); the last two patterns put the new
-    maximum into the second part, after the first part has already been multiplied by V."""
+    later P underflow to zero) and a single late spike.  The pipelined kernel takes the exponentials of
+    a key tile against the reference it already has, in chunks of 32 keys, and only redoes them when a
+    score exceeds that reference by more than 2^8; the last two patterns put the new maximum into the
+    last chunk of a tile, or make it move with every chunk."""
     B, R, L = 2, 3, 128 * 6 + 50
     q, k, v = make_inputs(B, L, R * H, 1.0, 4000 + H)
     q = (q.float() * 0.05 + 1.0).half()                      # close to all-ones queries
@@ -284,6 +322,26 @@ def test_additive_mask(H, L):
     mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(1)).half()
     expected = oracle(q, k, v, H, mask)
     assert_close(run(q, k, v, H, mask=mask), expected)
+
+
+@pytest.mark.parametrize("L", [127, 200, 256, 1000])
+def test_additive_mask_rows_at_any_alignment(L):
+    """Mask rows are read with 16-byte loads when they start on a 16-byte boundary and value by value
+    otherwise (L not a multiple of 8, or a mask tensor that starts at an odd element)."""
+    H = 64
+    q, k, v = make_inputs(2, L, 3 * H, 1.0, 600 + L)
+    gen = torch.Generator().manual_seed(L)
+    mask = (0.5 * torch.randn(2, L, L, generator=gen)).half()
+    mask[0] += torch.triu(torch.full((L, L), float("-inf")), diagonal=1).half()
+    expected = oracle(q, k, v, H, mask)
+    assert_close(run(q, k, v, H, mask=mask), expected)
+    # the same values in a buffer whose first element is 2 bytes past a 16-byte boundary
+    store = torch.empty(mask.numel() + 8, dtype=torch.float16, device="cuda")
+    shifted = store[1:1 + mask.numel()].view_as(mask)
+    shifted.copy_(mask)
+    assert shifted.data_ptr() % 16 == 2
+    y = fa.attention_forward(H, 16, q.cuda(), k.cuda(), v.cuda(), shifted, flags=_lib.FLAG_SYNC)
+    assert_close(y.float().cpu(), expected)
 
 
 def test_value_of_ones_gives_ones_at_full_size():
@@ -437,6 +495,19 @@ def test_bounded_wait_gives_up_and_reports_without_harming_the_gpu():
     assert_close(run(q, k, v, 64), oracle(q, k, v, 64))
 
 
+def test_more_batch_entries_than_a_grid_axis_holds():
+    """70000 one-tile problems: the reference puts the batch on the x axis of its grid
+    (include/fused_attn.cuh:883) and takes such a shape; so does this launcher."""
+    B, L, H = 70000, 8, 16
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    q, k, v = (torch.randn(B, L, H, generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+    y = fa.attention_forward(H, 16, q, k, v, flags=_lib.FLAG_SYNC)
+    ref = torch.softmax(q.float() @ k.float().mT / H ** 0.5, -1) @ v.float()
+    d = (y.float() - ref).abs()
+    assert float(d.max()) <= MAX_ABS_TOL and float(d.mean()) <= MEAN_ABS_TOL
+
+
 # ---------------------------------------------------------------- drop-in module `fused_attn`
 def _fused_attn_module():
     ext_dir = os.path.join(os.path.dirname(fa.__file__), "ext")
@@ -481,10 +552,11 @@ def _ref_wmma():
     return lib
 
 
-def _run_ref_wmma(lib, q, k, v, H, C):
+def _run_ref_wmma(lib, q, k, v, H, C, mask=None):
     B, L, F = q.shape
     y_ref = torch.empty_like(q)
-    assert lib.ref_wmma_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, y_ref.data_ptr(),
+    assert lib.ref_wmma_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                          None if mask is None else mask.data_ptr(), y_ref.data_ptr(),
                                           B, L, F, H, C) == 0
     torch.cuda.synchronize()
     return y_ref
@@ -509,6 +581,32 @@ def test_against_the_reference_fused_kernel_on_its_own_test_shapes(H, C):
     if err_ref["max_abs"] <= 5e-3:
         torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
     assert err_new["max_abs"] <= err_ref["max_abs"], (err_new, err_ref)
+
+
+@pytest.mark.parametrize("H,C", [(64, 64), (64, 128), (128, 128), (32, 32), (16, 32), (128, 64)])
+def test_mask_against_the_reference_kernel_single_chunk(H, C):
+    """The mask semantics pinned to the reference itself.  Its kernel adds the mask tile only while it
+    works on the first key chunk (include/fused_attn.cuh:732-742), so with L == chunk_size, where the
+    first chunk is the whole key axis, it is a valid oracle for what the mask means: an additive
+    [B, L, L] array shared by all heads (include/fused_attn.cuh:686, 738).  Causal and padding masks
+    with soft values in between, no row masked out completely; the two kernels must agree at the
+    reference's rtol = atol = 1e-2 and this one must meet the fp32 oracle's bounds."""
+    lib = _ref_wmma()
+    B, R, L = 2, 2, C
+    hq, hk, hv = make_inputs(B, L, R * H, 1.0, 900 + H + C)
+    mask = torch.zeros(B, L, L, dtype=torch.float16)
+    mask[0] = torch.triu(torch.full((L, L), float("-inf")), diagonal=1).half()          # causal
+    mask[1, :, L - L // 4:] = float("-inf")                                               # padding
+    mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(C)).half()
+    q, k, v, dmask = hq.cuda(), hk.cuda(), hv.cuda(), mask.cuda()
+    expected = oracle(hq, hk, hv, H, mask)
+    y_ref = _run_ref_wmma(lib, q, k, v, H, C, dmask)
+    err_ref = error_metrics(y_ref.float().cpu(), expected)
+    assert err_ref["max_abs"] <= 1e-2, err_ref       # the reference kernel and the oracle formula mean the same mask
+    for flags in (0, SIMPLE):
+        y = fa.attention_forward(H, C, q, k, v, dmask, flags=flags | _lib.FLAG_SYNC)
+        torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
+        assert_close(y.float().cpu(), expected)
 
 
 @pytest.mark.parametrize("H,C,B,R,L", [(64, 64, 1, 4, 256), (128, 128, 2, 4, 512), (64, 128, 8, 12, 512)])
