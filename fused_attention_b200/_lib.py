@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = (
     "fa_b200_query",
     "fa_b200_read_status",
     "fa_b200_select_kernel",
+    "fa_b200_describe_schedule",
     "fa_b200_selftest_bounded_wait",
 )
 
@@ -81,6 +82,8 @@ def load() -> ctypes.CDLL:
         lib.fa_b200_selftest_bounded_wait.argtypes = [i32, ctypes.POINTER(ctypes.c_uint32)]
         lib.fa_b200_select_kernel.restype = i32
         lib.fa_b200_select_kernel.argtypes = [u32, u32, u32, u32, i32, u32]
+        lib.fa_b200_describe_schedule.restype = i32
+        lib.fa_b200_describe_schedule.argtypes = [u32, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint32)]
         _lib = lib
         return lib
 

@@ -120,3 +120,31 @@ def select_kernel(B: int, L: int, F: int, head_dim: int, has_mask: bool = False,
     if rc < 0:
         _lib.check(rc)
     return {1: "simple", 2: "pipelined"}[rc]
+
+
+def describe_schedule(B: int, L: int, F: int, head_dim: int, flags: int = 0, sm_count: int = 148) -> dict:
+    """How the warp-specialised kernel spreads a call over its CTAs (``fa_b200_describe_schedule``)."""
+    o = (ctypes.c_uint32 * 7)()
+    _lib.check(_lib.load().fa_b200_describe_schedule(B, L, F, head_dim, int(flags), int(sm_count), o))
+    return {"kernel": {1: "simple", 2: "pipelined"}[o[0]], "grid": o[1], "full_rounds": o[2],
+            "tail_items": o[3], "tail_steps": o[4], "key_steps": o[5], "tail_grid": o[6]}
+
+
+def cta_segments(sched: dict, n_items: int, cta: int) -> list[tuple[int, int, int]]:
+    """The (work item, first key step, key steps) runs that CTA ``cta`` works through under ``sched``, in
+    the kernel's order and with its arithmetic: whole items round-robin, then its share of a divided
+    round (at most two runs)."""
+    grid, n, T = sched["grid"], sched["key_steps"], sched["tail_steps"]
+    if T == 0:
+        return [(item, 0, n) for item in range(cta, n_items, grid)]
+    segs = [(cta + k * grid, 0, n) for k in range(sched["full_rounds"])]
+    tg = sched["tail_grid"]
+    a, b = (cta * T // tg, (cta + 1) * T // tg) if cta < tg else (0, 0)
+    base = sched["full_rounds"] * grid
+    if b > a:
+        t0, j0 = divmod(a, n)
+        len0 = min(n - j0, b - a)
+        segs.append((base + t0, j0, len0))
+        if b - a > len0:
+            segs.append((base + t0 + 1, 0, b - a - len0))
+    return segs

@@ -26,11 +26,30 @@ constexpr int kMaxDevices = 64;
 constexpr int kHostChunks = 8;   // pipeline depth of the host-buffer entry point
 constexpr int kStatusWords = 4;  // device status block, see fa::WaitCtl
 
+// bytes of one split-scratch buffer for a device with `sms` SMs: numerators, {max, sum} pairs, counters
+size_t split_o_bytes(int sms) { return static_cast<size_t>(2 * sms) * 2 * (128 / 4) * fa::kTile * sizeof(float4); }
+size_t split_ml_bytes(int sms) { return static_cast<size_t>(2 * sms) * 2 * fa::kTile * sizeof(float2); }
+size_t split_cnt_bytes(int sms) { return static_cast<size_t>(sms) * 2 * 4 * sizeof(uint32_t); }
+
+struct SplitScratch {
+    bool taken = false;
+    cudaStream_t stream = nullptr;
+    float4* o = nullptr;       // fa::Params::part_o
+    float2* ml = nullptr;      // fa::Params::part_ml
+    uint32_t* cnt = nullptr;   // fa::Params::part_cnt
+};
+constexpr int kSplitPool = 4;
+
 struct DeviceCtx {
     bool ready = false;
     int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
     uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count, id of the launch that reported, -}
     std::atomic<uint32_t> attr_done{0};   // bit per kernel instance whose smem attribute is set
+    // Scratch of launches that divide their last round of work items (fa::Plan): one buffer per stream,
+    // because launches on different streams may run at the same time.  kSplitPool buffers are allocated
+    // with the context; a launch on a stream that finds none free runs undivided.
+    std::mutex split_mu;
+    SplitScratch split[kSplitPool];
     // host-buffer entry point: copy-in / compute / copy-out streams, per-chunk events and
     // grow-on-demand staging buffers
     std::mutex host_mu;   // one host-buffer call at a time per device: they share the staging buffers
@@ -44,6 +63,13 @@ DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mu;
 std::atomic<uint32_t> g_launch_id{0};   // every launch gets its own non-zero id (Params::launch_id)
 
+int fold_status(uint32_t* status_dev, uint32_t* const* counters, int n_counters, size_t counter_bytes);
+int fold_ctx_status(DeviceCtx& c) {
+    uint32_t* counters[kSplitPool];
+    for (int i = 0; i < kSplitPool; ++i) counters[i] = c.split[i].cnt;
+    return fold_status(c.status, counters, kSplitPool, split_cnt_bytes(c.sm_count));
+}
+
 uint32_t next_launch_id() {
     uint32_t id = g_launch_id.fetch_add(1, std::memory_order_relaxed) + 1u;
     if (id == 0) id = g_launch_id.fetch_add(1, std::memory_order_relaxed) + 1u;
@@ -52,12 +78,15 @@ uint32_t next_launch_id() {
 
 // Read the device status block after the stream has been synchronised; a report is cleared once it
 // has been returned, so that it is given to one caller and later calls start clean.
-int fold_status(uint32_t* status_dev) {
+// (A launch that gave up may have left the part counters of a divided round half counted: they are
+// zeroed with the report.)
+int fold_status(uint32_t* status_dev, uint32_t* const* counters, int n_counters, size_t counter_bytes) {
     uint32_t w[2] = {0, 0};
     cudaError_t e = cudaMemcpy(w, status_dev, sizeof(w), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (w[0] == 0) return FA_B200_OK;
     e = cudaMemset(status_dev, 0, 2 * sizeof(uint32_t));
+    for (int i = 0; i < n_counters && e == cudaSuccess; ++i) e = cudaMemset(counters[i], 0, counter_bytes);
     return e != cudaSuccess ? static_cast<int>(e) : FA_B200_ERR_DEVICE_TIMEOUT;
 }
 
@@ -67,10 +96,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-unsigned long long* g_trace_buf = nullptr;  // device buffer of 8 * 512 records, set by the trace hook
-uint32_t g_trace_cta = 0;
+#ifdef FA_CYCLES
+unsigned long long* g_cycles_buf = nullptr;  // device buffer of two clock values, set by fa_b200_debug_cycles
 #endif
+
 
 // Caller holds g_mu and has made `device` current.
 int ensure_ctx(int device, DeviceCtx** out) {
@@ -88,6 +117,17 @@ int ensure_ctx(int device, DeviceCtx** out) {
         if (e != cudaSuccess) return static_cast<int>(e);
         e = cudaMemset(c.status, 0, kStatusWords * sizeof(uint32_t));
         if (e != cudaSuccess) return static_cast<int>(e);
+        for (int i = 0; i < kSplitPool; ++i) {
+            char* base = nullptr;
+            const size_t ob = split_o_bytes(c.sm_count), mb = split_ml_bytes(c.sm_count), cb = split_cnt_bytes(c.sm_count);
+            e = cudaMalloc(reinterpret_cast<void**>(&base), ob + mb + cb);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            c.split[i].o = reinterpret_cast<float4*>(base);
+            c.split[i].ml = reinterpret_cast<float2*>(base + ob);
+            c.split[i].cnt = reinterpret_cast<uint32_t*>(base + ob + mb);
+            e = cudaMemset(c.split[i].cnt, 0, cb);
+            if (e != cudaSuccess) return static_cast<int>(e);
+        }
         c.ready = true;
     }
     if (g_encode == nullptr) {
@@ -145,7 +185,7 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
                            FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT;
     if (flags & ~known) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
-    if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && (mask || H < 64)) return FA_B200_ERR_FLAGS;
+    if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && H < 64) return FA_B200_ERR_FLAGS;
     return FA_B200_OK;
 }
 
@@ -154,7 +194,8 @@ int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask,
                   int sm_count) {
     if (flags & FA_B200_FLAG_FORCE_SIMPLE) return 1;
     if (flags & FA_B200_FLAG_FORCE_PIPELINED) return 2;
-    if (has_mask || H < 64) return 1;
+    (void)has_mask;   // both kernels take the additive mask
+    if (H < 64) return 1;
     // The pipelined kernel works on items of two query tiles (256 rows) on persistent CTAs.  It wins
     // as soon as there are enough items to occupy a good part of the SMs (measured: 39 vs 57 us on
     // B=64 R=16 L=197 H=64); a single partial tile or a handful of items goes to the simple kernel,
@@ -167,6 +208,51 @@ int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask,
     if (L > 5 * 128) return 2;
     if (pairs * 2 < static_cast<uint64_t>(sm_count)) return 1;
     return 2;
+}
+
+// How the pipelined kernel's work items are spread over its CTAs (fa::Plan).
+struct Schedule {
+    uint32_t grid;         // CTAs
+    uint32_t full_rounds;  // rounds of whole items
+    uint32_t tail_items;   // items of the divided last round (0 = nothing divided)
+    uint32_t tail_steps;   // tail_items * n
+    uint32_t tail_grid;    // CTAs that share the tail key steps
+};
+
+// n_items work items of n key steps each on a device with `sms` SMs.  Undivided: min(sms, n_items) CTAs
+// take whole items round-robin.  When the last round would leave most SMs idle, the key steps of its r
+// items are dealt out evenly instead: each of the first tail_grid CTAs gets a contiguous range of them (at
+// most two items touched) and the parts of an item are merged in the kernel.  tail_grid = min(sms, 2 r): a
+// range is then at least half an item, so no item has more than three parts (what the kernel's merge is
+// built for).  Dividing has a price, measured at about five key steps per CTA (one more segment boundary,
+// the hand-over of a part through L2 and the merge, which reads 128 KB per other part of an item): it is
+// done when what it saves beyond that is at least a twentieth of the CTA's work.
+constexpr uint32_t kSplitCostSteps = 5;
+Schedule make_schedule(uint32_t n_items, uint32_t n, uint32_t sms, bool allow_split) {
+    Schedule s;
+    s.grid = n_items < sms ? n_items : sms;
+    s.full_rounds = (n_items + s.grid - 1) / s.grid;
+    s.tail_items = 0;
+    s.tail_steps = 0;
+    s.tail_grid = 0;
+    if (!allow_split || sms == 0 || n < 2) return s;
+    const uint32_t r = n_items % sms;
+    if (r == 0) return s;
+    const uint32_t tg = 2u * r < sms ? 2u * r : sms;
+    const uint64_t T = static_cast<uint64_t>(r) * n;
+    if (T * tg > 0xFFFFFFFFull) return s;                 // the kernel's range arithmetic is 32-bit
+    const uint32_t most = static_cast<uint32_t>((T + tg - 1) / tg);   // key steps of the busiest tail CTA
+    const uint32_t least = static_cast<uint32_t>(T / tg);
+    const uint64_t undivided = static_cast<uint64_t>(s.full_rounds) * n;          // key steps of the busiest CTA, whole items
+    const uint64_t gain_needed = kSplitCostSteps + (undivided / 20 > 1 ? undivided / 20 : 1);
+    if (static_cast<uint64_t>(most) + gain_needed >= n) return s;
+    if (2u * least + 2u <= n) return s;                   // four parts would fit (cannot happen with tail_grid <= 2 r: guard)
+    s.grid = n_items < sms ? tg : sms;
+    s.full_rounds = n_items / sms;
+    s.tail_items = r;
+    s.tail_steps = static_cast<uint32_t>(T);
+    s.tail_grid = tg;
+    return s;
 }
 
 // Launch with or without the programmatic-stream-serialization attribute.  With it the kernel's
@@ -203,20 +289,41 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
-template <int H>
+template <int H, bool M>
 int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
-                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, cudaStream_t st, bool overlap) {
+                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, uint32_t n_ctas,
+                     cudaStream_t st, bool overlap) {
     constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
-    auto kern = fa::fa_fwd_pipelined<H>;
+    auto kern = fa::fa_fwd_pipelined<H, M>;
     if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
         c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
-    const uint32_t sms = static_cast<uint32_t>(c.sm_count);
-    const dim3 grid(p.n_items < sms ? p.n_items : sms, 1, 1);   // persistent: one CTA per SM
+    const dim3 grid(n_ctas, 1, 1);   // persistent: at most one CTA per SM
     const cudaError_t e = launch_kernel(kern, grid, 512, smem, st, overlap, mq, mk, mv, my, p);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+// The split-scratch buffer of `st` on this device: the one it already has, else a free one, else none.
+// None also while the stream is being captured.
+const SplitScratch* scratch_for_stream(DeviceCtx& c, cudaStream_t st) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (cap != cudaStreamCaptureStatusNone) return nullptr;
+    std::lock_guard<std::mutex> lk(c.split_mu);
+    for (int i = 0; i < kSplitPool; ++i)
+        if (c.split[i].taken && c.split[i].stream == st) return &c.split[i];
+    for (int i = 0; i < kSplitPool; ++i)
+        if (!c.split[i].taken) {
+            c.split[i].taken = true;
+            c.split[i].stream = st;
+            return &c.split[i];
+        }
+    return nullptr;
 }
 
 // Device-pointer launch on `st`.  Caller holds no lock.
@@ -258,19 +365,43 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.n_items = p.q_pairs * p.R * B;
                 p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
                 p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-                p.trace = g_trace_buf;
-                p.trace_cta = g_trace_cta;
+#ifdef FA_CYCLES
+                p.cycles = g_cycles_buf;
 #endif
+                p.full_rounds = p.tail_items = p.tail_steps = p.tail_grid = 0;
+                p.part_o = nullptr;
+                p.part_ml = nullptr;
+                p.part_cnt = nullptr;
                 const int which = select_kernel(B, L, F, H, mask != nullptr, flags, c->sm_count);
                 const bool overlap = (flags & FA_B200_FLAG_NO_OVERLAP) == 0;
                 if (which == 2) {
+                    // Dividing the last round needs scratch that no other launch is using: the buffer that
+                    // belongs to this stream.  A stream that is being captured gets none (the recorded launch
+                    // could later be replayed next to anything).
+                    const SplitScratch* scratch = nullptr;
+                    if (!(flags & FA_B200_FLAG_NO_SPLIT)) scratch = scratch_for_stream(*c, st);
+                    const Schedule sch = make_schedule(p.n_items, p.n_kv_tiles, static_cast<uint32_t>(c->sm_count),
+                                                       scratch != nullptr);
+                    p.full_rounds = sch.full_rounds;
+                    p.tail_items = sch.tail_items;
+                    p.tail_steps = sch.tail_steps;
+                    p.tail_grid = sch.tail_grid;
+                    if (sch.tail_steps != 0) {
+                        p.part_o = scratch->o;
+                        p.part_ml = scratch->ml;
+                        p.part_cnt = scratch->cnt;
+                    }
                     // Y as a TMA store target: boxes of 32 rows x 64 columns (one epilogue warp each)
                     CUtensorMap my;
                     rc = make_map(&my, y, B, L, F, H, 32);
-                    if (rc == FA_B200_OK)
-                        rc = H == 128 ? launch_pipelined<128>(*c, 8, mq, mk, mv, my, p, st, overlap)
-                                      : launch_pipelined<64>(*c, 9, mq, mk, mv, my, p, st, overlap);
+                    if (rc == FA_B200_OK) {
+                        if (mask)
+                            rc = H == 128 ? launch_pipelined<128, true>(*c, 10, mq, mk, mv, my, p, sch.grid, st, overlap)
+                                          : launch_pipelined<64, true>(*c, 11, mq, mk, mv, my, p, sch.grid, st, overlap);
+                        else
+                            rc = H == 128 ? launch_pipelined<128, false>(*c, 8, mq, mk, mv, my, p, sch.grid, st, overlap)
+                                          : launch_pipelined<64, false>(*c, 9, mq, mk, mv, my, p, sch.grid, st, overlap);
+                    }
                 } else if (mask) {
                     switch (H) {
                         case 16: rc = launch_simple<16, true>(*c, 4, mq, mk, mv, p, st, overlap); break;
@@ -291,7 +422,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
     }
     if (rc == FA_B200_OK && (flags & FA_B200_FLAG_SYNC)) {
         e = cudaStreamSynchronize(st);
-        rc = e != cudaSuccess ? static_cast<int>(e) : fold_status(c->status);
+        rc = e != cudaSuccess ? static_cast<int>(e) : fold_ctx_status(*c);
     }
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
@@ -428,9 +559,12 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
         p.n_items = p.q_pairs * p.R * B;
         p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
         p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-        p.trace = nullptr;
-        p.trace_cta = 0;
+        p.full_rounds = p.tail_items = p.tail_steps = p.tail_grid = 0;
+        p.part_o = nullptr;
+        p.part_ml = nullptr;
+        p.part_cnt = nullptr;
+#ifdef FA_CYCLES
+        p.cycles = nullptr;
 #endif
         if (mask_or_null) {
             switch (H) {
@@ -527,12 +661,13 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
         const uint32_t n_chunks = units < kHostChunks ? units : kHostChunks;
         const __half* hsrc[3] = {static_cast<const __half*>(q), static_cast<const __half*>(k),
                                  static_cast<const __half*>(v)};
-        // every chunk runs the kernel the whole problem would get, so the result has the same
-        // bits as one device-pointer call on the full tensors
+        // every chunk runs the kernel the whole problem would get, with every work item undivided, so
+        // the result has the same bits as one device-pointer call on the full tensors with
+        // FA_B200_FLAG_NO_SPLIT
         // (plain launches: a chunk's kernel is ordered behind copies on other streams, not behind a kernel)
         const uint32_t chunk_flags =
             (flags & ~static_cast<uint32_t>(FA_B200_FLAG_SYNC | FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED)) |
-            FA_B200_FLAG_NO_OVERLAP |
+            FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT |
             (select_kernel(B, L, F, H, mask_or_null != nullptr, flags, c->sm_count) == 2 ? FA_B200_FLAG_FORCE_PIPELINED
                                                                                        : FA_B200_FLAG_FORCE_SIMPLE);
         if (mbytes && !by_batch) {   // the mask is shared by all heads: one copy ahead of everything
@@ -596,7 +731,7 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v, 
         if (rc == FA_B200_OK && e1 != cudaSuccess) rc = static_cast<int>(e1);
         if (rc == FA_B200_OK && e2 != cudaSuccess) rc = static_cast<int>(e2);
         if (rc == FA_B200_OK && e3 != cudaSuccess) rc = static_cast<int>(e3);
-        if (rc == FA_B200_OK) rc = fold_status(c->status);
+        if (rc == FA_B200_OK) rc = fold_ctx_status(*c);
     }
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
@@ -650,6 +785,9 @@ int fa_b200_read_status(int device, uint32_t out[2]) {
         e = cudaDeviceSynchronize();
         if (e == cudaSuccess) e = cudaMemcpy(out, c->status, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
         if (e == cudaSuccess) e = cudaMemset(c->status, 0, kStatusWords * sizeof(uint32_t));
+        if (e == cudaSuccess && (out[0] != 0 || out[1] != 0))
+            for (int i = 0; i < kSplitPool && e == cudaSuccess; ++i)
+                e = cudaMemset(c->split[i].cnt, 0, split_cnt_bytes(c->sm_count));
         if (e != cudaSuccess) rc = static_cast<int>(e);
     }
     if (prev != device) (void)cudaSetDevice(prev);
@@ -679,14 +817,38 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]) {
     return rc;
 }
 
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-// Trace builds only: choose the recording CTA and the device buffer (8 * 512 * 8 bytes).
-int fa_b200_trace_setup(void* device_buffer, uint32_t cta) {
-    g_trace_buf = static_cast<unsigned long long*>(device_buffer);
-    g_trace_cta = cta;
+#ifdef FA_CYCLES
+// -DFA_CYCLES builds only: CTA 0 of the pipelined kernel writes its time stamps here (64 records of 4 u64).
+int fa_b200_debug_cycles(void* device_buffer_of_256_u64) {
+    g_cycles_buf = static_cast<unsigned long long*>(device_buffer_of_256_u64);
     return FA_B200_OK;
 }
 #endif
+
+int fa_b200_describe_schedule(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim, uint32_t flags,
+                              uint32_t sm_count, uint32_t out[7]) {
+    if (!out) return FA_B200_ERR_NULL_POINTER;
+    alignas(16) static const char d[16] = {0};
+    const int rc = validate(d, d, d, nullptr, d, B, L, F, head_dim, 0, flags);
+    if (rc != FA_B200_OK) return rc;
+    const uint32_t n = (L + fa::kTile - 1) / fa::kTile;
+    const uint32_t n_items = ((L + 2 * fa::kTile - 1) / (2 * fa::kTile)) * (F / head_dim) * B;
+    const int which = select_kernel(B, L, F, head_dim, false, flags, static_cast<int>(sm_count));
+    out[0] = static_cast<uint32_t>(which);
+    out[5] = n;
+    if (which != 2) {
+        out[1] = n * (F / head_dim) * B;
+        out[2] = out[3] = out[4] = out[6] = 0;
+        return FA_B200_OK;
+    }
+    const Schedule s = make_schedule(n_items, n, sm_count, (flags & FA_B200_FLAG_NO_SPLIT) == 0);
+    out[1] = s.grid;
+    out[2] = s.full_rounds;
+    out[3] = s.tail_items;
+    out[4] = s.tail_steps;
+    out[6] = s.tail_grid;
+    return FA_B200_OK;
+}
 
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim, int has_mask,
                           uint32_t flags) {

@@ -45,30 +45,19 @@ struct Params {
     uint32_t n_items;     // q_pairs * R * B: work items of the pipelined kernel
     float scale_log2;     // log2(e) / sqrt(H)
     float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-    unsigned long long* trace;  // [8 slots][512] (clock64 << 8 | tag) of one CTA, see FA_TRACE_EV
-    uint32_t trace_cta;         // linear block index that records
+    // schedule of the pipelined kernel (see Plan) and the scratch of a divided tail round
+    uint32_t full_rounds;  // rounds of whole items: item = cta + k * grid
+    uint32_t tail_items;   // items after the full rounds whose key steps are divided among the CTAs
+    uint32_t tail_steps;   // tail_items * n_kv_tiles, or 0 when nothing is divided
+    uint32_t tail_grid;    // the first tail_grid CTAs share the tail key steps (at most the grid)
+    float4* part_o;        // [2 * grid slots][2 tiles][H/4][128 rows] numerators of partial segments, fp32
+    float2* part_ml;       // [2 * grid slots][2 tiles][128 rows] {reference maximum, row sum}
+    uint32_t* part_cnt;    // [tail item][2 tiles][4 warps] parts counted in; zero between launches
+#ifdef FA_CYCLES
+    unsigned long long* cycles;  // 64 records (launch_id % 64) of CTA 0: {globaltimer at entry, globaltimer after the
+                                 // wait for the previous kernel, globaltimer at the end, clock64 from that wait to the end}
 #endif
 };
-
-// Compile with -DFA_TRACE to make one CTA of the pipelined kernel record a time line: every role
-// (slot) appends clock64() with a tag at its hand-over points.  Off in normal builds.
-#ifdef FA_TRACE
-#define FA_TRACE_DECL                                                                              \
-    uint32_t tr_n = 0;                                                                             \
-    const bool tr_on = p.trace != nullptr &&                                                       \
-        (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == p.trace_cta;
-#define FA_TRACE_EV(slot, tag)                                                                     \
-    do {                                                                                           \
-        if (tr_on && tr_n < 512) {                                                                 \
-            p.trace[(slot) * 512 + tr_n] = (static_cast<unsigned long long>(clock64()) << 8) | (tag); \
-            ++tr_n;                                                                                \
-        }                                                                                          \
-    } while (0)
-#else
-#define FA_TRACE_DECL
-#define FA_TRACE_EV(slot, tag) do {} while (0)
-#endif
 
 constexpr int kTile = 128;  // rows of a query tile and of a key/value tile
 
@@ -90,6 +79,14 @@ struct TileGeom {
     static constexpr int kBoxBytes = kTile * kBoxCols * 2;     // 16 KiB at H >= 64
     static constexpr int kTileBytes = kTile * H * 2;
 };
+
+// Ask for one tile (all its boxes) to be brought into L2.
+template <int H>
+__device__ __forceinline__ void prefetch_tile_l2(const CUtensorMap* map, int32_t col0, int32_t row0, int32_t batch) {
+    using G = TileGeom<H>;
+#pragma unroll
+    for (int b = 0; b < G::kBoxes; ++b) tma_prefetch_l2_3d(map, col0 + b * G::kBoxCols, row0, batch);
+}
 
 // One TMA tile (all its boxes) -> shared memory at `dst`, signalling `bar`.
 template <int H>
@@ -497,10 +494,10 @@ struct PipeCfg {
     static constexpr int kStageBytes = 4 * 32 * 128;   // epilogue staging: per warp 32 rows x 64 fp16
     static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
-    // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+H) O1 [384,384+H)
-    // P (fp16, 64 columns per tile) has columns of its own instead of overwriting its S: the next
-    // Q K^T of a tile then does not have to wait for the P V that reads P, only for the softmax warps
-    // to have read S, and a tile's softmax passes follow one another without its MMAs in between.
+    // TMEM columns.  P (fp16, 64 columns per tile) has columns of its own instead of overwriting its
+    // S: the next Q K^T of a tile then does not have to wait for the P V that reads P, only for the
+    // softmax warps to have read S, and a tile's softmax passes follow one another without its MMAs
+    // in between.
     //   H = 64:   S0 [0,128)  S1 [128,256)  O0 [256,320)  P0 [320,384)  O1 [384,448)  P1 [448,512)
     //   H = 128:  S  [0,128) shared by the two tiles, which use it in turn (scores only live from the
     //             Q K^T until the softmax warps have read them), P0 [128,192)  P1 [192,256)
@@ -517,31 +514,352 @@ struct PipeCfg {
     static constexpr int kHeldChunks = H == 128 ? 1 : 0;
 };
 
-// Persistent: grid = min(number of SMs, work items), block = 512.  A work item is one pair of
-// 128-row query tiles of one (batch, head); CTA c takes items c, c + grid, c + 2*grid, ...  Items
-// are numbered query-pair fastest, so the CTAs running at any moment share few heads and their
-// K/V tiles stay in L2.  Every role walks the same item list; the key steps of consecutive items
-// form one continuous sequence of "global steps", so the two-tile ping-pong never drains: while
-// the epilogue warps store item k, the MMA and softmax warps are already in item k+1.
+// Into how many parts the key axis of one work item may be divided (see Plan).
+constexpr uint32_t kMaxParts = 3;
+
+// What one CTA of the pipelined kernel does: a list of SEGMENTS, each a run of consecutive key steps
+// of one work item (a pair of 128-row query tiles of one (batch, head)).
+//   - `whole` segments are whole items (all n key steps), taken round-robin: item = cta + k * grid.
+//     Items are numbered query-pair fastest, so the CTAs running at any moment share few heads and
+//     their K/V tiles stay in L2.  They come before the CTA's tail segments (below).
+//   - When the items do not fill a whole number of rounds, the launcher may divide the last, partial
+//     round (Params::tail_items items after full_rounds * grid, T = tail_steps = tail_items * n key
+//     steps in all) evenly among the first tg = Params::tail_grid CTAs: CTA c < tg takes the tail key
+//     steps [c*T/tg, (c+1)*T/tg), numbered item by item.  That range is never longer than n, so it
+//     touches at most two items: up to two tail segments, the first ending an item (or lying inside
+//     one), the second starting the next item at step 0; and never shorter than n/2, so no item is
+//     cut into more than three parts.
+// A segment that does not cover all n key steps is PARTIAL: its epilogue does not write Y but adds
+// its (reference maximum, row sum, numerator) to the item's other parts, see the epilogue role.
+struct Plan {
+    uint32_t whole;     // whole-item segments of this CTA: segments 0 .. whole-1
+    uint32_t ntail;     // tail segments of this CTA (0, 1 or 2): segments whole .. nseg-1
+    uint32_t nseg;      // all segments of this CTA
+    uint32_t steps;     // all key steps of this CTA
+    uint32_t t_item0;   // first tail segment: index of its item among the tail items,
+    uint32_t t_j00;     //   its first key step,
+    uint32_t t_len0;    //   its length (0 = no tail segment)
+    uint32_t t_len1;    // second tail segment: item t_item0 + 1 from key step 0, this long (0 = none)
+};
+
+__device__ __forceinline__ Plan make_plan(const Params& p) {
+    Plan pl;
+    const uint32_t n = p.n_kv_tiles, grid = gridDim.x, c = blockIdx.x;
+    pl.t_item0 = pl.t_j00 = pl.t_len0 = pl.t_len1 = 0;
+    if (p.tail_steps == 0) {
+        pl.whole = c < p.n_items ? (p.n_items - c + grid - 1u) / grid : 0u;
+    } else {
+        pl.whole = p.full_rounds;
+        const uint32_t tg = p.tail_grid;                       // the launcher keeps tail_steps * tail_grid below 2^32
+        const uint32_t a = c < tg ? c * p.tail_steps / tg : 0u;
+        const uint32_t b = c < tg ? (c + 1u) * p.tail_steps / tg : 0u;
+        if (b > a) {
+            pl.t_item0 = a / n;
+            pl.t_j00 = a - pl.t_item0 * n;
+            pl.t_len0 = min(n - pl.t_j00, b - a);
+            pl.t_len1 = (b - a) - pl.t_len0;
+        }
+    }
+    pl.ntail = (pl.t_len0 ? 1u : 0u) + (pl.t_len1 ? 1u : 0u);
+    pl.nseg = pl.whole + pl.ntail;
+    pl.steps = pl.whole * n + pl.t_len0 + pl.t_len1;
+    return pl;
+}
+
+struct Seg {
+    uint32_t item;       // work item: q_pair = item % q_pairs, (batch, head) = item / q_pairs
+    uint32_t j0, len;    // key steps [j0, j0 + len)
+    bool partial;        // fewer than all n key steps
+};
+// Of a tail segment k (k >= t0 = number of whole segments): index of its item among the tail items; this
+// CTA's scratch slot for the part (two per CTA).  Looked up where they are needed rather than kept in
+// registers.
+template <typename PlanRef>
+__device__ __forceinline__ uint32_t seg_tail_item(PlanRef& pl, uint32_t t0, uint32_t k) { return pl.t_item0 + (k - t0); }
+__device__ __forceinline__ uint32_t seg_slot(uint32_t t0, uint32_t k) { return 2u * blockIdx.x + (k - t0); }
+
+__device__ __forceinline__ uint32_t seg_len(const Plan& pl, const Params& p, uint32_t k) {
+    return k < pl.whole ? p.n_kv_tiles : (k == pl.whole ? pl.t_len0 : pl.t_len1);
+}
+
+// `pl` may be the CTA's copy in shared memory (volatile: the tail fields are then read where they are
+// used, once per tail segment, instead of being kept in registers through a role's loops).
+template <typename PlanRef>
+__device__ __forceinline__ Seg get_seg(PlanRef& pl, uint32_t t0, const Params& p, uint32_t k) {
+    Seg s;
+    if (k < t0) {
+        s.item = blockIdx.x + k * gridDim.x;
+        s.j0 = 0;
+        s.len = p.n_kv_tiles;
+        s.partial = false;
+    } else {
+        const uint32_t t = k - t0;   // 0 or 1
+        s.j0 = t ? 0u : pl.t_j00;
+        s.len = t ? pl.t_len1 : pl.t_len0;
+        s.item = p.full_rounds * gridDim.x + pl.t_item0 + t;
+        s.partial = s.len != p.n_kv_tiles;
+    }
+    return s;
+}
+
+// The CTA whose tail range holds tail key step `step` (ranges are [c*T/tg, (c+1)*T/tg)).
+// The launcher only divides a round when T * tg fits in 32 bits.
+__device__ __forceinline__ uint32_t tail_cta_of(uint32_t step, uint32_t T, uint32_t tg) {
+    return ((step + 1u) * tg - 1u) / T;
+}
+
+// ---- a divided work item: hand-over and merge of its parts -------------------------------------
+// Scratch of one (slot, tile): H/4 columns of float4, each 128 rows long, so that the 32 lanes of a
+// warp (32 consecutive rows) write and read 512 consecutive bytes.  {reference maximum, row sum} of a
+// row lie beside it in part_ml.  Indices stay below 2^32 (the whole scratch is a few tens of MB).
+template <int H>
+__device__ __forceinline__ uint32_t part_o_index(uint32_t slot, uint32_t tile, uint32_t row) {
+    return (slot * 2u + tile) * ((H / 4) * kTile) + row;
+}
+
+// Rows of O (one per thread: TMEM lane) -> this part's scratch slot, fp32, not normalised.
+// `after_last_load` runs once the tile has left TMEM (hand the O columns back there).
+template <int H, typename F>
+__device__ __forceinline__ void store_part(const Params& p, uint32_t tO, uint32_t slot, uint32_t tile,
+                                           uint32_t row, float m, float l, F after_last_load) {
+    const uint32_t po = part_o_index<H>(slot, tile, row);
+#pragma unroll
+    for (int c = 0; c < H / 16; ++c) {
+        float o[16];
+        tmem_ld16(tO + c * 16, o);
+        tmem_wait_ld();
+        if (c == H / 16 - 1) after_last_load();
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            p.part_o[po + (c * 4 + v) * kTile] = make_float4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+    }
+    p.part_ml[(slot * 2u + tile) * kTile + row] = make_float2(m, l);
+}
+
+// The parts of tail item `tail_item` are the tail segments of consecutive CTAs c_first ... c_last.
+struct PartsOf {
+    uint32_t c_first, parts;
+};
+__device__ __forceinline__ PartsOf parts_of(const Params& p, uint32_t tail_item) {
+    const uint32_t n = p.n_kv_tiles, T = p.tail_steps;
+    PartsOf r;
+    r.c_first = tail_cta_of(tail_item * n, T, p.tail_grid);
+    r.parts = min(tail_cta_of(tail_item * n + n - 1u, T, p.tail_grid) - r.c_first + 1u, kMaxParts);
+    return r;
+}
+// Scratch slot of part `pp`: CTA c_first + pp computed it as its first tail segment if that CTA's
+// range begins inside this item, else as its second.
+__device__ __forceinline__ uint32_t slot_of_part(const Params& p, uint32_t tail_item, uint32_t c_first, uint32_t pp) {
+    const uint32_t cta = c_first + pp;
+    const uint32_t a = cta * p.tail_steps / p.tail_grid;
+    return 2u * cta + (a / p.n_kv_tiles == tail_item ? 0u : 1u);
+}
+
+// The common case, two parts: the rows of part `mine` (0 or 1) are in TMEM at tO, the other part is read
+// from scratch.  All of the other part is asked for first and `wait_for_o` runs while it is on its way (the
+// caller waits there for the last P V if its rows are not complete yet).  Same arithmetic, in the same
+// order, as merge_parts.
+template <int H, typename F>
+__device__ __forceinline__ void merge_two(const Params& p, uint32_t tail_item, uint32_t c_first, uint32_t tile,
+                                          uint32_t row, uint32_t mine, uint32_t tO, float m_mine, float l_mine,
+                                          __half* y_row, bool row_valid, F wait_for_o) {
+    const uint32_t other = slot_of_part(p, tail_item, c_first, 1u - mine);
+    const float2 ml_o = __ldcg(p.part_ml + (other * 2u + tile) * kTile + row);
+    const float4* src = p.part_o + part_o_index<H>(other, tile, row);
+    float4 x[H / 4];
+#pragma unroll
+    for (int c = 0; c < H / 4; ++c) x[c] = __ldcg(src + c * kTile);
+    wait_for_o();
+    float m_all = fmaxf(m_mine, ml_o.x);
+    if (m_all == -INFINITY) m_all = 0.f;
+    const float w_m = ex2_approx((m_mine - m_all) * p.scale_log2);
+    const float w_o = ex2_approx((ml_o.x - m_all) * p.scale_log2);
+    const bool first = mine == 0u;   // parts are added in the order of the key axis
+    const float w0 = first ? w_m : w_o, w1 = first ? w_o : w_m;
+    const float inv_l = 1.f / fmaf(w1, first ? ml_o.y : l_mine, fmaf(w0, first ? l_mine : ml_o.y, 0.f));
+#pragma unroll
+    for (int q = 0; q < H / 32; ++q) {
+        float o[32];
+        tmem_ld32(tO + q * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float xs[4] = {x[q * 8 + c].x, x[q * 8 + c].y, x[q * 8 + c].z, x[q * 8 + c].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float a0 = first ? o[4 * c + e] : xs[e], a1 = first ? xs[e] : o[4 * c + e];
+                o[4 * c + e] = fmaf(w1, a1, fmaf(w0, a0, 0.f)) * inv_l;
+            }
+        }
+        if (row_valid) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+                uint4 wv;
+                wv.x = pack_half2(o[e], o[e + 1]);
+                wv.y = pack_half2(o[e + 2], o[e + 3]);
+                wv.z = pack_half2(o[e + 4], o[e + 5]);
+                wv.w = pack_half2(o[e + 6], o[e + 7]);
+                *reinterpret_cast<uint4*>(y_row + q * 32 + e) = wv;
+            }
+        }
+    }
+}
+
+// Add up the parts of 32 rows of one tile of a divided item and write Y.  One thread per row, run by
+// a softmax warp (it has the registers to keep a whole row of another part, or half a row of two other
+// parts, in flight).  The parts are added in the order of the key axis whoever does the adding, so the
+// result does not depend on which part happened to finish last:
+//   Y = sum_p w_p O_p / sum_p w_p l_p,   w_p = 2^((m_p - max_q m_q) * scale_log2).
+// `mine` is the index of the part whose rows are still in TMEM at tO (with reference m_mine and row
+// sum l_mine), or kMaxParts if every part is read from scratch.  An item has two or three parts.
+template <int H>
+__device__ __forceinline__ void merge_parts(const Params& p, uint32_t tail_item, uint32_t tile, uint32_t row,
+                                            uint32_t mine, uint32_t tO, float m_mine, float l_mine,
+                                            __half* y_row, bool row_valid) {
+    const PartsOf po = parts_of(p, tail_item);
+    if (po.parts == 2u && mine < 2u) {
+        merge_two<H>(p, tail_item, po.c_first, tile, row, mine, tO, m_mine, l_mine, y_row, row_valid, [] {});
+        return;
+    }
+    uint32_t slot[3];
+    float mp[3], lp[3];
+#pragma unroll
+    for (uint32_t pp = 0; pp < 3; ++pp) {
+        slot[pp] = pp < po.parts ? slot_of_part(p, tail_item, po.c_first, pp) : 0u;
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (pp < po.parts) ml = pp == mine ? make_float2(m_mine, l_mine) : __ldcg(p.part_ml + (slot[pp] * 2u + tile) * kTile + row);
+        mp[pp] = ml.x;
+        lp[pp] = ml.y;
+    }
+    float m_all = fmaxf(fmaxf(mp[0], mp[1]), mp[2]);
+    if (m_all == -INFINITY) m_all = 0.f;   // a row masked out in every part: weights 0, Y = 0/0 as torch.softmax gives
+    float w[3], l_all = 0.f;
+#pragma unroll
+    for (uint32_t pp = 0; pp < 3; ++pp) {
+        w[pp] = pp < po.parts ? ex2_approx((mp[pp] - m_all) * p.scale_log2) : 0.f;
+        if (pp < po.parts) l_all = fmaf(w[pp], lp[pp], l_all);
+    }
+    const float inv_l = 1.f / l_all;
+    if (po.parts == 3u && mine < 3u) {
+        // Three parts, one of them in TMEM: half a row of both others in flight at a time.  In key order
+        // the parts are (o, a, b), (a, o, b) or (a, b, o) with o the one in TMEM.
+        const uint32_t sa = mine == 0u ? slot[1] : slot[0], sb = mine == 2u ? slot[1] : slot[2];
+#pragma unroll 1
+        for (int half = 0; half < H / 64; ++half) {
+            float xa[64], xb[64];
+            const float4* pa = p.part_o + part_o_index<H>(sa, tile, row) + (half * 16) * kTile;
+            const float4* pb = p.part_o + part_o_index<H>(sb, tile, row) + (half * 16) * kTile;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 v = __ldcg(pa + c * kTile);
+                xa[4 * c] = v.x; xa[4 * c + 1] = v.y; xa[4 * c + 2] = v.z; xa[4 * c + 3] = v.w;
+            }
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 v = __ldcg(pb + c * kTile);
+                xb[4 * c] = v.x; xb[4 * c + 1] = v.y; xb[4 * c + 2] = v.z; xb[4 * c + 3] = v.w;
+            }
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                float o[32];
+                tmem_ld32(tO + half * 64 + sub * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float a = xa[sub * 32 + e], bq = xb[sub * 32 + e];
+                    const float v0 = mine == 0u ? o[e] : a;
+                    const float v1 = mine == 0u ? a : (mine == 1u ? o[e] : bq);
+                    const float v2 = mine == 2u ? o[e] : bq;
+                    o[e] = fmaf(w[2], v2, fmaf(w[1], v1, fmaf(w[0], v0, 0.f))) * inv_l;
+                }
+                if (row_valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 wv;
+                        wv.x = pack_half2(o[e], o[e + 1]);
+                        wv.y = pack_half2(o[e + 2], o[e + 3]);
+                        wv.z = pack_half2(o[e + 4], o[e + 5]);
+                        wv.w = pack_half2(o[e + 6], o[e + 7]);
+                        *reinterpret_cast<uint4*>(y_row + half * 64 + sub * 32 + e) = wv;
+                    }
+                }
+            }
+        }
+        return;
+    }
+    // Every part from scratch (an epilogue warp's part was the last of its item): half a row of two
+    // parts in flight at a time, the third, if there is one, behind them.
+#pragma unroll 1
+    for (int half = 0; half < H / 64; ++half) {
+        float xa[64], xb[64];
+        const float4* pa = p.part_o + part_o_index<H>(slot[0], tile, row) + (half * 16) * kTile;
+        const float4* pb = p.part_o + part_o_index<H>(slot[1], tile, row) + (half * 16) * kTile;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float4 v = __ldcg(pa + c * kTile);
+            xa[4 * c] = v.x; xa[4 * c + 1] = v.y; xa[4 * c + 2] = v.z; xa[4 * c + 3] = v.w;
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float4 v = __ldcg(pb + c * kTile);
+            xb[4 * c] = v.x; xb[4 * c + 1] = v.y; xb[4 * c + 2] = v.z; xb[4 * c + 3] = v.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 64; ++e) xa[e] = fmaf(w[1], xb[e], fmaf(w[0], xa[e], 0.f));
+        if (po.parts > 2u) {
+            const float4* pc = p.part_o + part_o_index<H>(slot[2], tile, row) + (half * 16) * kTile;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 v = __ldcg(pc + c * kTile);
+                xb[4 * c] = v.x; xb[4 * c + 1] = v.y; xb[4 * c + 2] = v.z; xb[4 * c + 3] = v.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 64; ++e) xa[e] = fmaf(w[2], xb[e], xa[e]);
+        }
+        if (row_valid) {
+#pragma unroll
+            for (int e = 0; e < 64; e += 8) {
+                uint4 wv;
+                wv.x = pack_half2(xa[e] * inv_l, xa[e + 1] * inv_l);
+                wv.y = pack_half2(xa[e + 2] * inv_l, xa[e + 3] * inv_l);
+                wv.z = pack_half2(xa[e + 4] * inv_l, xa[e + 5] * inv_l);
+                wv.w = pack_half2(xa[e + 6] * inv_l, xa[e + 7] * inv_l);
+                *reinterpret_cast<uint4*>(y_row + half * 64 + e) = wv;
+            }
+        }
+    }
+}
+
+// Persistent: grid = min(number of SMs, work items) (the number of SMs when the tail round is
+// divided), block = 512.  Every role walks the same list of segments (Plan); the key steps of
+// consecutive segments form one continuous sequence of "global steps", so the two-tile ping-pong
+// never drains: while the epilogue warps finish segment k, the MMA and softmax warps are already in
+// segment k+1.
 //
 // warps 0-3: softmax of query tile 0; 4-7: softmax of tile 1 (each also rescales its O rows in
-// the rare steps whose reference maximum moves); 8-11: epilogue (Y = O / l);
-// 12: MMA issue (one elected lane) and TMEM owner; 13: TMA producer (one lane); 14: second MMA
-// issuing warp at H = 128 (12 issues Q K^T, 14 issues P V); 15: idle.
+// the rare steps whose reference maximum moves); 8-11: epilogue (Y = O / l, or the hand-over and
+// merge of a partial segment); 12: MMA issue (one elected lane) and TMEM owner; 13: TMA producer
+// (one lane); 14: second MMA issuing warp at H = 128 (12 issues Q K^T, 14 issues P V); 15: idle.
 //
 // Per tile and key step: Q K^T -> S; the softmax warps read S into registers and say so (SFREE),
 // which lets the next Q K^T into the S buffer; they write P into the tile's P columns once the
 // previous step's P V has read them (PV); P V accumulates into O.  Nothing of a tile's next Q K^T
-// waits for its P V.
+// waits for its P V.  With kHasMask the softmax warps add the additive mask row (read with 16-byte
+// loads) to the scores they have just read.
 //
 // Barrier phases (the parity to wait for is the low bit of the index):
-//   per global step g = k*n + j:  S_i (MMA -> softmax), SFREE (softmax -> MMA; at H = 128 one
-//                barrier whose phase is the use 2g + i of the shared S buffer), P_i (softmax -> MMA),
-//                PV_i (MMA -> softmax and, for the item's last step, epilogue)
-//   per item k:  QFULL_i (TMA -> MMA), QEMPTY_i (MMA -> TMA), A_i (softmax -> epilogue),
+//   per global step g:  S_i (MMA -> softmax), SFREE (softmax -> MMA; at H = 128 one barrier whose
+//                phase is the use 2g + i of the shared S buffer), P_i (softmax -> MMA),
+//                PV_i (MMA -> softmax and, for the segment's last step, epilogue)
+//   per segment k:  QFULL_i (TMA -> MMA), QEMPTY_i (MMA -> TMA), A_i (softmax -> epilogue),
 //                OFREE_i (epilogue -> MMA and softmax)
-//   per ring item t (K0 V0 K1 V1 ... across items):  FULL[t % NS], EMPTY[t % NS]
-template <int H>
+//   per ring item t (K0 V0 K1 V1 ... across segments):  FULL[t % NS], EMPTY[t % NS]
+//
+// Build with -DFA_CYCLES to make CTA 0 record, per launch, the global timer at its entry, after its wait
+// for the previous kernel and at its end, and its SM clock count in between, in Params::cycles (a
+// diagnostic: the clock count compares versions of the kernel independently of the clock the GPU happens
+// to run at, the timer shows the gaps between launches; absent from normal builds).
+template <int H, bool kHasMask>
 __global__ void __launch_bounds__(512, 1)
 fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmY,
@@ -551,7 +869,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr int NS = C::kStages;
     enum {
         BAR_QFULL0 = 0, BAR_QFULL1,  // TMA -> MMA: query tile landed
-        BAR_QEMPTY0, BAR_QEMPTY1,    // MMA -> TMA: the item's last Q K^T of this tile has retired
+        BAR_QEMPTY0, BAR_QEMPTY1,    // MMA -> TMA: the segment's last Q K^T of this tile has retired
         BAR_S0, BAR_S1,              // MMA -> softmax: S tile complete
         BAR_P0, BAR_P1,              // softmax -> MMA: P written (and O rescaled in the rare steps
                                      // that need it); 4 arrivals, one per softmax warp
@@ -560,6 +878,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_PV0, BAR_PV1,            // MMA -> softmax (P buffer free, O at rest) and epilogue: P V complete
         BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
         BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
+        BAR_EPI,                     // epilogue -> softmax: the epilogue warps are through (4 arrivals)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FINAL2,                  // the same for the second issuing warp
         BAR_FULL,                    // NS ring barriers TMA -> MMA
@@ -569,16 +888,21 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[BAR_COUNT];
-    __shared__ float l_buf[2][2][kTile];  // [item parity][tile][row] final row sums
+    __shared__ float l_buf[2][2][kTile];  // [segment parity][tile][row] final row sums
+    __shared__ float m_buf[2][2][kTile];  // ... and the reference maxima they are relative to
+    __shared__ uint32_t deferred[2][4];            // [tile][row quarter]: the epilogue warps' part (first of two tail segments) was the last of its item
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_flag;
 
     const uint32_t tid = threadIdx.x;
+#ifdef FA_CYCLES
+    if (p.cycles != nullptr && blockIdx.x == 0 && tid == 0) p.cycles[4 * (p.launch_id & 63u)] = global_timer_ns();
+#endif
     const uint32_t warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
     const uint32_t lane = tid & 31u;
-    const uint32_t n = p.n_kv_tiles;
-    const uint32_t n_items = p.n_items;
     const uint32_t q_pairs = p.q_pairs;
+    __shared__ Plan plan_smem;
+    volatile Plan& pl_s = plan_smem;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;                   // two tiles
@@ -588,6 +912,28 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto bar = [&](int i) { return bar0 + 8u * i; };
     const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles, p.status + 2, p.launch_id};
 
+    if (tid == 13 * 32) {
+        // The plan of this CTA, and a request for the tiles it needs first to be brought into L2.  In a
+        // launch that overlaps the previous kernel of the stream this CTA may be here long before that
+        // kernel completes; a prefetch returns nothing to the SM, and L2 is where that kernel's writes
+        // land, so whatever it still writes is what the loads after the wait below will read.
+        const Plan mine = make_plan(p);
+        plan_smem = mine;
+        if (mine.nseg > 0u) {
+            const Seg sg = get_seg(mine, mine.whole, p, 0);
+            const uint32_t bh = sg.item / q_pairs;
+            const int32_t col0 = static_cast<int32_t>((bh % p.R) * H), batch = static_cast<int32_t>(bh / p.R);
+            const int32_t q_row0 = static_cast<int32_t>((sg.item % q_pairs) * 2u * kTile);
+            prefetch_tile_l2<H>(&tmQ, col0, q_row0, batch);
+            prefetch_tile_l2<H>(&tmK, col0, static_cast<int32_t>(sg.j0 * kTile), batch);
+            prefetch_tile_l2<H>(&tmQ, col0, q_row0 + kTile, batch);
+            prefetch_tile_l2<H>(&tmV, col0, static_cast<int32_t>(sg.j0 * kTile), batch);
+            if (sg.len > 1u) {
+                prefetch_tile_l2<H>(&tmK, col0, static_cast<int32_t>((sg.j0 + 1u) * kTile), batch);
+                prefetch_tile_l2<H>(&tmV, col0, static_cast<int32_t>((sg.j0 + 1u) * kTile), batch);
+            }
+        }
+    }
     if (tid == 0) {
         prefetch_tensormap(&tmY);
 #pragma unroll
@@ -595,11 +941,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
             const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_SFREE0 || i == BAR_SFREE1 ||
-                                   i == BAR_A0 || i == BAR_A1 ||
+                                   i == BAR_A0 || i == BAR_A1 || i == BAR_EPI ||
                                    i == BAR_OFREE0 || i == BAR_OFREE1);
             mbar_init(bar(i), per_warp ? 4u : 1u);
         }
         abort_flag = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) (&deferred[0][0])[i] = 0;
         fence_mbar_init();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
@@ -612,16 +960,21 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // Barriers, TMEM and descriptors are set up; nothing of global memory has been touched yet.  In a
-    // launch that was allowed to overlap the previous kernel of the stream, wait here for that kernel
-    // to complete, then let the next launch's CTAs take the SMs this grid's CTAs leave (they will
-    // stop at this same point: the overlap is never deeper than one launch).
+    // Barriers, TMEM and descriptors are set up; nothing of global memory has been read or written yet.
+    // In a launch that was allowed to overlap the previous kernel of the stream, wait here for that
+    // kernel to complete, then let the next launch's CTAs take the SMs this grid's CTAs leave (they
+    // will stop at this same point: the overlap is never deeper than one launch).
     grid_dep_wait();
     grid_dep_launch();
     if (tid == 15 * 32) leave_early_if_launch_failed(ctl);   // warp 15 has no other work
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512] = static_cast<unsigned long long>(clock64());
+    const uint32_t nseg = pl_s.nseg, ntail = pl_s.ntail, t0 = nseg - ntail;   // t0: first tail segment
+#ifdef FA_CYCLES
+    long long cyc0 = 0;
+    if (p.cycles != nullptr && blockIdx.x == 0 && tid == 0) {
+        p.cycles[4 * (p.launch_id & 63u) + 1] = global_timer_ns();
+        cyc0 = clock64();
+    }
 #endif
 
     if (warp < 8) {
@@ -634,20 +987,29 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tP = tmem_base + lane_off + (i ? C::kColP1 : C::kColP0);
         const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
         const float c = p.scale_log2;
-        FA_TRACE_DECL
-        const bool tr_me = row == 0;
         uint32_t g = 0;   // global step
-        uint32_t k = 0;   // item count of this CTA
-        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
-            float m = -INFINITY, l = 0.f;
-            for (uint32_t j = 0; j < n; ++j, ++g) {
+        float m = -INFINITY, l = 0.f;
+        for (uint32_t k = 0; k < nseg; ++k) {
+            const Seg sg = get_seg(pl_s, t0, p, k);
+            m = -INFINITY;
+            l = 0.f;
+            // with a mask: the row of mask[batch] this thread adds to its scores
+            const __half* mask_row = nullptr;
+            bool mask_vec = false;
+            if constexpr (kHasMask) {
+                const uint32_t q_row = ((sg.item % q_pairs) * 2u + i) * kTile + row;
+                const uint32_t batch = (sg.item / q_pairs) / p.R;
+                if (q_row < p.L) mask_row = p.mask + (static_cast<size_t>(batch) * p.L + q_row) * p.L;
+                mask_vec = ((p.L & 7u) | (reinterpret_cast<uintptr_t>(p.mask) & 15u)) == 0u;
+            }
+            for (uint32_t jj = 0; jj < sg.len; ++jj, ++g) {
+                const uint32_t j = sg.j0 + jj;
                 mbar_wait(bar(BAR_S0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
                 tc_fence_after();
                 __syncwarp();
-                if (tr_me) FA_TRACE_EV(1 + i, 1);   // S ready
                 float s[kTile];
                 const bool ragged = (j + 1) * kTile > p.L;
-                const bool first = j == 0;
+                const bool first = jj == 0;
                 load_s_row(tS, s);
                 // S is in registers: the MMA warp may overwrite it with the next scores.
                 tc_fence_before();
@@ -661,17 +1023,25 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         tc_fence_after();
                     }
                 }
+                if constexpr (kHasMask) {
+                    if (mask_row != nullptr)
+                        add_mask_row(s, mask_row + static_cast<size_t>(j) * kTile,
+                                     min(static_cast<int>(p.L - j * kTile), kTile), p.mask_to_score, mask_vec);
+                }
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
-                if (first) m = row_max(s);   // first key tile: the reference is its row maximum
-                if (tr_me) FA_TRACE_EV(1 + i, 2);   // S in registers
+                if (first) m = row_max(s);   // first key tile of the segment: the reference is its row maximum
                 // Exponentials against the standing reference, with the maximum of the scores taken
                 // in the same pass.  The reference only has to move when a score exceeds it by more
                 // than 2^8 in the exp2 domain.  P has one buffer per tile and the previous step's P V
                 // may still be reading it: the first chunks' exponentials go to registers meanwhile.
                 {
+                    // A row that has seen nothing but -inf so far (possible only with a mask) takes 0 as
+                    // the reference of its exponents, so that P = 0 and l = 0 instead of inf - inf.
+                    float nmc = -m * c;
+                    if constexpr (kHasMask) nmc = (m == -INFINITY) ? 0.f : nmc;
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     uint32_t held[16 * (C::kHeldChunks > 0 ? C::kHeldChunks : 1)];
-                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, -m * c, tP, mx4, held);
+                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, nmc, tP, mx4, held);
                     if constexpr (C::kHeldChunks > 0) {
                         if (g > 0) {
                             mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
@@ -680,7 +1050,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
 #pragma unroll
                     for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
-                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, -m * c, tP, mx4);
+                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, nmc, tP, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -690,101 +1060,210 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const float m_new = moved ? mx : m;
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
+                        float nmc2 = -m * c;
+                        if constexpr (kHasMask) nmc2 = (m == -INFINITY) ? 0.f : nmc2;
                         float unused[4];
-                        l = l * alpha + exp_chunks<0, 4, false>(s, c, -m * c, tP, unused);
+                        l = l * alpha + exp_chunks<0, 4, false>(s, c, nmc2, tP, unused);
                         // (This wait returns at once.  It is here because with a branch point at this
                         // place of the rare path the compiler allocates the common path without spills.)
                         if (g > 0) mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
-                        rescale_o_row<H>(tO, alpha);
+                        if (!first) rescale_o_row<H>(tO, alpha);   // the segment's first P V overwrites O
                     } else {
                         l += sum;
                     }
                 }
-                if (tr_me) FA_TRACE_EV(1 + i, 5);   // exponentials issued
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_P0 + i));
-                if (tr_me) FA_TRACE_EV(1 + i, 4);   // P signalled
             }
-            // Hand the row sums to the epilogue.  The A barrier may run at most one phase ahead of
-            // the epilogue's wait, so the previous item's O must have been read out first (always
-            // true already when an item has two or more key steps).
+            // Hand the row sums (and the references they are relative to) to the epilogue.  The A
+            // barrier may run at most one phase ahead of the epilogue's wait, so the previous segment's
+            // O must have been read out first (always true already when a segment has two or more
+            // key steps).
             if (k > 0) mbar_wait(bar(BAR_OFREE0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OFREE0 + i));
             l_buf[k & 1u][i][row] = l;
+            m_buf[k & 1u][i][row] = m;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
         }
+        // ---- parts of divided items ---------------------------------------------------------------
+        // If this CTA's last segment is a part of a divided item, these warps finish it themselves:
+        // they have nothing else left to do, they have the registers to keep many loads in flight, and
+        // the part's rows can come straight from TMEM.  A warp that finds every other part of its 32
+        // rows already counted in adds the parts up and writes Y; otherwise it leaves its rows in the
+        // CTA's scratch slot and counts itself in (and adds up after all if that made it the last).
+        const uint32_t wq = warp & 3u;
+        if (ntail > 0u) {   // the CTA's last segment is a tail segment
+            const Seg sg = get_seg(pl_s, t0, p, nseg - 1u);
+            if (sg.partial) {
+                const uint32_t tail_item = seg_tail_item(pl_s, t0, nseg - 1u);
+                const PartsOf po = parts_of(p, tail_item);
+                const uint32_t mine = blockIdx.x - po.c_first;
+                uint32_t* cnt = p.part_cnt + (tail_item * 2u + i) * 4u + wq;
+                const uint32_t q_row = ((sg.item % q_pairs) * 2u + i) * kTile + row;
+                const uint32_t bh = sg.item / q_pairs;
+                __half* y_row = p.y + (static_cast<size_t>(bh / p.R) * p.L + q_row) * p.F + (bh % p.R) * H;
+                auto wait_for_o = [&] {   // the last P V: this tile's O rows are complete
+                    mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+                    tc_fence_after();
+                    __syncwarp();
+                };
+                // The counter is looked at while the last P V is still running.  Parts are counted in only
+                // when they are complete, so "every other part is in" stays true once it has been seen.
+                uint32_t seen = 0;
+                if (lane == 0) seen = ld_acquire_gpu(cnt);
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                bool last = seen + 1u == po.parts;
+                if (last && po.parts == 2u) {
+                    merge_two<H>(p, tail_item, po.c_first, i, row, mine, tO, m, l, y_row, q_row < p.L, wait_for_o);
+                } else {
+                    wait_for_o();
+                    if (!last) {
+                        store_part<H>(p, tO, seg_slot(t0, nseg - 1u), i, row, m, l, [] {});
+                        __threadfence();    // the part is complete once every lane's stores are visible to the device
+                        __syncwarp();
+                        uint32_t arrived = 0;
+                        if (lane == 0) arrived = atomicAdd(cnt, 1u);
+                        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                        last = arrived + 1u == po.parts;
+                        if (last) __threadfence();
+                    }
+                    if (last)
+                        merge_parts<H>(p, tail_item, i, row, mine, tO, m, l, y_row, q_row < p.L);
+                }
+                if (last) {
+                    __syncwarp();
+                    if (lane == 0) atomicExch(cnt, 0u);   // the counter is left at zero for the next launch
+                }
+            }
+        }
+        // A part that the epilogue warps put into scratch (the first tail segment of a CTA that has two) and
+        // that turned out to be the last of its item: added up here, every part read from scratch.
+        if (ntail == 2u) {
+            mbar_wait_relaxed(bar(BAR_EPI), 0, ctl, kRoleSoftmax | BAR_EPI, 100);
+            if (deferred[i][wq] != 0u) {
+                const Seg sg = get_seg(pl_s, t0, p, t0);
+                const uint32_t q_row = ((sg.item % q_pairs) * 2u + i) * kTile + row;
+                const uint32_t bh = sg.item / q_pairs;
+                __half* y_row = p.y + (static_cast<size_t>(bh / p.R) * p.L + q_row) * p.F + (bh % p.R) * H;
+                const uint32_t tail_item = seg_tail_item(pl_s, t0, t0);
+                __threadfence();
+                merge_parts<H>(p, tail_item, i, row, kMaxParts, tO, 0.f, 0.f, y_row, q_row < p.L);
+                __syncwarp();
+                if (lane == 0) atomicExch(p.part_cnt + (tail_item * 2u + i) * 4u + wq, 0u);
+            }
+        }
     } else if (warp < 12) {
-        // ------------------------------------------------------------------ epilogue: Y = O / l
-        // Each warp owns 32 rows of the tile.  It reads them from TMEM 64 columns at a time, scales
-        // by 1/l, rounds to fp16 and writes 16-byte vectors into its 4 KiB staging buffer (rows of
-        // 128 bytes, 128-byte swizzle), which one TMA store sends to Y: the warp is not held up by
-        // scattered global stores and the O tile is handed back as soon as it is in registers.
+        // ------------------------------------------------------------------ epilogue
+        // Each warp owns 32 rows of the tile.
+        // Whole item: it reads them from TMEM, scales by 1/l, rounds to fp16 and writes 16-byte vectors
+        // into its 4 KiB staging buffer (rows of 128 bytes, 128-byte swizzle), which one TMA store
+        // sends to Y: the warp is not held up by scattered global stores and the O tile is handed
+        // back as soon as it is in registers.
+        // Part of a divided item that is not the CTA's last segment: the rows go to this CTA's scratch
+        // slot as they are (fp32, not normalised) together with (reference maximum, row sum), and the
+        // warp counts itself in on the item's counter (see store_part, merge_parts).
         setmaxnreg_dec<64>();
         const uint32_t row = tid & 127u;
         const uint32_t wq = warp & 3u;
         const uint32_t lane_off = (wq * 32u) << 16;
         const uint32_t stage = sStage + wq * 4096u;
-        uint32_t k = 0;
-        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
-            const uint32_t q_pair = item % q_pairs, bh = item / q_pairs;
+        uint32_t g_end = 0;   // global steps up to and including the current segment
+        for (uint32_t k = 0; k < nseg; ++k) {
+            const Seg sg = get_seg(pl_s, t0, p, k);
+            if (sg.partial && k + 1u == nseg) break;   // the softmax warps finish a final part themselves
+            g_end += sg.len;
+            const uint32_t q_pair = sg.item % q_pairs, bh = sg.item / q_pairs;
             const uint32_t head = bh % p.R, batch = bh / p.R;
 #pragma unroll
             for (uint32_t i = 0; i < 2; ++i) {
-                // this wait lasts for a whole item: poll every 100 ns
+                // this wait lasts for a whole segment: poll every 100 ns
                 mbar_wait_relaxed(bar(BAR_A0 + i), k & 1u, ctl, kRoleEpilogue | (BAR_A0 + i), 100);
-                const float inv_l = 1.f / l_buf[k & 1u][i][row];
-                // The item's last P V of this tile.  Every earlier phase of this barrier has
+                const float l_row = l_buf[k & 1u][i][row];
+                // The segment's last P V of this tile.  Every earlier phase of this barrier has
                 // completed by the time the softmax warps signalled and the next phase needs this
                 // epilogue's OFREE arrival, so the parity test is unambiguous.
-                mbar_wait(bar(BAR_PV0 + i), (k * n + n - 1u) & 1u, ctl, kRoleEpilogue | (BAR_PV0 + i));
+                mbar_wait(bar(BAR_PV0 + i), (g_end - 1u) & 1u, ctl, kRoleEpilogue | (BAR_PV0 + i));
                 tc_fence_after();
                 __syncwarp();
                 const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
                 const int32_t row0 = static_cast<int32_t>((q_pair * 2u + i) * kTile + wq * 32u);
+                if (!sg.partial) {
+                    const float inv_l = 1.f / l_row;
 #pragma unroll
-                for (int half = 0; half < H / 64; ++half) {
-                    // the previous store out of this staging buffer must have read it completely
-                    if (lane == 0) bulk_wait_read_all();
-                    __syncwarp();
+                    for (int half = 0; half < H / 64; ++half) {
+                        // the previous store out of this staging buffer must have read it completely
+                        if (lane == 0) bulk_wait_read_all();
+                        __syncwarp();
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {   // 16 columns at a time keeps this role within 64 registers
-                        float o[16];
-                        tmem_ld16(tO + half * 64 + c * 16, o);
-                        tmem_wait_ld();
-                        if (half == H / 64 - 1 && c == 3) {
-                            // the whole O tile has left TMEM: the MMA warp may overwrite it
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+                        for (int c = 0; c < 4; ++c) {   // 16 columns at a time keeps this role within 64 registers
+                            float o[16];
+                            tmem_ld16(tO + half * 64 + c * 16, o);
+                            tmem_wait_ld();
+                            if (half == H / 64 - 1 && c == 3) {
+                                // the whole O tile has left TMEM: the MMA warp may overwrite it
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+                            }
+#pragma unroll
+                            for (int v4 = 0; v4 < 2; ++v4) {
+                                const uint32_t w0 = pack_half2(o[v4 * 8 + 0] * inv_l, o[v4 * 8 + 1] * inv_l);
+                                const uint32_t w1 = pack_half2(o[v4 * 8 + 2] * inv_l, o[v4 * 8 + 3] * inv_l);
+                                const uint32_t w2 = pack_half2(o[v4 * 8 + 4] * inv_l, o[v4 * 8 + 5] * inv_l);
+                                const uint32_t w3 = pack_half2(o[v4 * 8 + 6] * inv_l, o[v4 * 8 + 7] * inv_l);
+                                // logical 16-byte chunk c*2+v4 of row `lane`, 128-byte swizzle
+                                const uint32_t chunk = static_cast<uint32_t>(c * 2 + v4) ^ (lane & 7u);
+                                st_shared_v4(stage + lane * 128u + chunk * 16u, w0, w1, w2, w3);
+                            }
                         }
-#pragma unroll
-                        for (int v4 = 0; v4 < 2; ++v4) {
-                            const uint32_t w0 = pack_half2(o[v4 * 8 + 0] * inv_l, o[v4 * 8 + 1] * inv_l);
-                            const uint32_t w1 = pack_half2(o[v4 * 8 + 2] * inv_l, o[v4 * 8 + 3] * inv_l);
-                            const uint32_t w2 = pack_half2(o[v4 * 8 + 4] * inv_l, o[v4 * 8 + 5] * inv_l);
-                            const uint32_t w3 = pack_half2(o[v4 * 8 + 6] * inv_l, o[v4 * 8 + 7] * inv_l);
-                            // logical 16-byte chunk c*2+v4 of row `lane`, 128-byte swizzle
-                            const uint32_t chunk = static_cast<uint32_t>(c * 2 + v4) ^ (lane & 7u);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128u + chunk * 16u),
-                                         "r"(w0), "r"(w1), "r"(w2), "r"(w3)
-                                         : "memory");
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && row0 < static_cast<int32_t>(p.L)) {   // rows past L are clipped by the store
+                            tma_store_3d(&tmY, stage, static_cast<int32_t>(head * H + half * 64), row0,
+                                         static_cast<int32_t>(batch));
+                            bulk_commit_group();
                         }
                     }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0 && row0 < static_cast<int32_t>(p.L)) {   // rows past L are clipped by the store
-                        tma_store_3d(&tmY, stage, static_cast<int32_t>(head * H + half * 64), row0,
-                                     static_cast<int32_t>(batch));
-                        bulk_commit_group();
-                    }
+                } else {
+                    // A tail segment that is not the CTA's last segment: the rows go to the scratch slot as
+                    // they are and the O tile is handed back.
+                    store_part<H>(p, tO, seg_slot(t0, k), i, row, m_buf[k & 1u][i][row], l_row, [&] {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(BAR_OFREE0 + i));
+                    });
                 }
             }
+            if (sg.partial) {
+                // Both O tiles have been handed back (the next segment's P V are not held up by what
+                // follows).  Once every lane's stores are visible to the device the warp counts itself in
+                // on the item's two counters.  If that makes its part the last of the item, the softmax warp
+                // of these rows adds the parts up at the end of the kernel (it has the registers to do it in
+                // a few trips to L2, and by then every part has long been complete).
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t tail_item = seg_tail_item(pl_s, t0, k);
+                    const PartsOf po = parts_of(p, tail_item);
+#pragma unroll
+                    for (uint32_t i = 0; i < 2; ++i)
+                        if (atomicAdd(p.part_cnt + (tail_item * 2u + i) * 4u + wq, 1u) + 1u == po.parts)
+                            deferred[i][wq] = 1u;
+                }
+            }
+            // the one tail segment this role takes is through: the softmax warps may look at the flags
+            if (sg.partial) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_EPI));
+            }
         }
-        if (lane == 0) bulk_wait_all();   // Y is complete before the CTA leaves
+        // The staging buffers must have been read before the CTA gives up its shared memory; the writes
+        // to Y themselves are complete, like every other write, when the grid is.
+        if (lane == 0) bulk_wait_read_all();
     } else {
         setmaxnreg_dec<80>();
         if (warp == 12 || (C::kTwoIssuers && warp == 14)) {
@@ -803,75 +1282,67 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // Once one of this warp's waits has given up (`ok` false) it issues nothing more: what it
             // would multiply has not arrived.
             bool ok = true;
-            auto mwait = [&](uint32_t b, uint32_t parity, const WaitCtl& wc, uint32_t code) {
-                ok &= mbar_wait(b, parity, wc, code);
+            auto mwait = [&](uint32_t b, uint32_t parity, uint32_t code) {
+                ok &= mbar_wait(b, parity, ctl, kRoleMma | code);
             };
-            auto wait_full = [&](uint32_t t) {
-                mwait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, ctl, kRoleMma | (BAR_FULL + (t % NS)));
-            };
+            auto wait_full = [&](uint32_t t) { mwait(bar(BAR_FULL + (t % NS)), (t / NS) & 1u, BAR_FULL + (t % NS)); };
             auto free_slot = [&](uint32_t t) { tc_commit(bar(BAR_EMPTY + (t % NS))); };
-#ifdef FA_TRACE
-            uint32_t tr_n = 0;
-            const bool tr_on = leader && p.trace != nullptr && blockIdx.x == p.trace_cta;
-#endif
-            const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
-            const uint32_t steps = my_items * n;   // global steps of this CTA
+            Plan pl;   // this role keeps the plan in registers: it may not wait for shared memory between MMAs
+            pl.ntail = ntail; pl.whole = t0; pl.nseg = nseg; pl.steps = pl_s.steps; pl.t_item0 = 0; pl.t_j00 = 0;
+            pl.t_len0 = pl_s.t_len0; pl.t_len1 = pl_s.t_len1;
+            const uint32_t steps = pl.steps;   // global steps of this CTA
             // ring item 2g is the K tile of global step g, item 2g+1 its V tile
+            // (k, j, len): segment of the step a loop is working on, its position in it, its length
+            uint32_t k = 0, j = 0, len = seg_len(pl, p, 0);
             if (steps > 0 && warp == 12) {
                 // S tiles of the very first step
-                mwait(bar(BAR_QFULL0), 0, ctl, kRoleMma | BAR_QFULL0);
+                mwait(bar(BAR_QFULL0), 0, BAR_QFULL0);
                 wait_full(0);
                 tc_fence_after();
                 if (leader && ok) {
                     issue_qk<H>(tS0, sQ, slot_addr(0));
                     tc_commit(bar(BAR_S0));
-                    if (n == 1) tc_commit(bar(BAR_QEMPTY0));
+                    if (len == 1) tc_commit(bar(BAR_QEMPTY0));
                 }
-                mwait(bar(BAR_QFULL1), 0, ctl, kRoleMma | BAR_QFULL1);
+                mwait(bar(BAR_QFULL1), 0, BAR_QFULL1);
                 // one S buffer for both tiles: tile 0's scores must have been read first
-                if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0, ctl, kRoleMma | BAR_SFREE0);
+                if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0, BAR_SFREE0);
                 tc_fence_after();
                 if (leader && ok) {
                     issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
                     tc_commit(bar(BAR_S1));
-                    if (n == 1) tc_commit(bar(BAR_QEMPTY1));
+                    if (len == 1) tc_commit(bar(BAR_QEMPTY1));
                     free_slot(0);
                 }
             }
-            uint32_t k = 0, j = 0;   // item and key step of global step g
             if constexpr (C::kTwoIssuers) {
                 mbar_poll_declare();
                 bool polled = false;
                 if (warp == 12) {
-                    // Q K^T stream: for every step g the scores of step g + 1, tile 0 then tile 1, each
-                    // as soon as the softmax warps have read what the S buffer holds.  That K has
-                    // landed is known long before; it is tested ahead of the previous step's last
-                    // MMAs and the answer read after them (mbar_poll_begin).
-                    for (uint32_t g = 0; g + 1 < steps; ++g) {
-                        const uint32_t tk = 2 * g + 2;
-                        const bool next_new_item = j + 1 == n;    // step g + 1 opens item k + 1
+                    // Q K^T stream: the scores of step q = 1, 2, ..., tile 0 then tile 1, each as soon as the
+                    // softmax warps have read what the S buffer holds.  That K has landed is known long
+                    // before; it is tested ahead of the previous step's last MMAs and the answer read
+                    // after them (mbar_poll_begin).
+                    for (uint32_t q = 1; q < steps; ++q) {
+                        bool new_seg = false;            // step q opens segment k
+                        if (++j == len) { j = 0; ++k; len = seg_len(pl, p, k); new_seg = true; }
+                        const bool last_of_seg = j + 1 == len;   // a segment's last Q K^T is its last use of the query tile
+                        const uint32_t tk = 2 * q;
                         if (!(polled && mbar_poll_end<0>())) wait_full(tk);
-                        if (next_new_item) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
-                        // With one S buffer its uses are numbered 2g + i (tile i, step g) and use u
-                        // needs the reading of use u - 1 (one barrier, phase = use); with one buffer
-                        // per tile the reading of step g of that tile.
-                        if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 1u, ctl, kRoleMma | BAR_SFREE0);
-                        else mwait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
-                        FA_TRACE_EV(0, 11);  // S0 read by the softmax warps
+                        if (new_seg) mwait(bar(BAR_QFULL0), k & 1u, BAR_QFULL0);
+                        // With one S buffer its uses are numbered 2q + i (tile i, step q) and use u
+                        // needs the reading of use u - 1 (one barrier, phase = use).
+                        mwait(bar(BAR_SFREE0), 1u, BAR_SFREE0);
                         tc_fence_after();
                         if (leader && ok) {
                             issue_qk<H>(tS0, sQ, slot_addr(tk));
                             tc_commit(bar(BAR_S0));
-                            // the Q K^T of an item's last key step is its last use of the query tile
-                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+                            if (last_of_seg) tc_commit(bar(BAR_QEMPTY0));
                         }
-                        FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
-                        if (next_new_item) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                        if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0u, ctl, kRoleMma | BAR_SFREE0);
-                        else mwait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
-                        FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
+                        if (new_seg) mwait(bar(BAR_QFULL1), k & 1u, BAR_QFULL1);
+                        mwait(bar(BAR_SFREE0), 0u, BAR_SFREE0);
                         tc_fence_after();
-                        polled = g + 2 < steps;
+                        polled = q + 1 < steps;
                         if (polled) {
                             const uint32_t nk = tk + 2;
                             mbar_poll_begin<0>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
@@ -879,11 +1350,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         if (leader && ok) {
                             issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                             tc_commit(bar(BAR_S1));
-                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
+                            if (last_of_seg) tc_commit(bar(BAR_QEMPTY1));
                             free_slot(tk);
                         }
-                        FA_TRACE_EV(0, 7);   // next Q K^T of tile 1 issued
-                        if (++j == n) { j = 0; ++k; }
                     }
                 } else {
                     // P V stream: for every step the products of tile 0 and tile 1 as their P arrive.
@@ -891,18 +1360,15 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const uint32_t tv = 2 * g + 1;
                         const uint32_t acc = j > 0 ? 1u : 0u;
                         if (!(polled && mbar_poll_end<1>())) wait_full(tv);
-                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
-                        mwait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
-                        FA_TRACE_EV(3, 2);   // P0 ready
+                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, BAR_OFREE0);
+                        mwait(bar(BAR_P0), g & 1u, BAR_P0);
                         tc_fence_after();
                         if (leader && ok) {
                             issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
                             tc_commit(bar(BAR_PV0));
                         }
-                        FA_TRACE_EV(3, 8);   // P V of tile 0 issued
-                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
-                        mwait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
-                        FA_TRACE_EV(3, 5);   // P1 ready
+                        if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, BAR_OFREE1);
+                        mwait(bar(BAR_P1), g & 1u, BAR_P1);
                         tc_fence_after();
                         polled = g + 1 < steps;
                         if (polled) {
@@ -914,8 +1380,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             tc_commit(bar(BAR_PV1));
                             free_slot(tv);
                         }
-                        FA_TRACE_EV(3, 10);  // P V of tile 1 issued
-                        if (++j == n) { j = 0; ++k; }
+                        if (++j == len) { j = 0; ++k; len = seg_len(pl, p, k); }
                     }
                 }
             } else {
@@ -928,8 +1393,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 bool polled = false;   // predicates 0-2 hold answers for this step
                 for (uint32_t g = 0; g < steps; ++g) {
                     const uint32_t tv = 2 * g + 1, tk = 2 * g + 2;
-                    const bool more = g + 1 < steps;          // a next global step exists
-                    const bool next_new_item = j + 1 == n;    // ... and it opens item k + 1
+                    const bool more = g + 1 < steps;            // a next global step exists
+                    const bool next_new_seg = j + 1 == len;     // ... and it opens segment k + 1
+                    // is the next step the last of its segment (its Q K^T the last use of the query tile)?
+                    const bool next_last_of_seg = next_new_seg ? seg_len(pl, p, k + 1u) == 1u : j + 2 == len;
                     const uint32_t acc = j > 0 ? 1u : 0u;
                     {
                         uint32_t ok_v = 0, ok_k = 0, ok_s0 = 0;
@@ -941,49 +1408,41 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         if (!ok_v) wait_full(tv);
                         if (more) {
                             if (!ok_k) wait_full(tk);
-                            if (next_new_item) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL0);
-                            if (!ok_s0) mwait(bar(BAR_SFREE0), g & 1u, ctl, kRoleMma | BAR_SFREE0);
+                            if (next_new_seg) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, BAR_QFULL0);
+                            if (!ok_s0) mwait(bar(BAR_SFREE0), g & 1u, BAR_SFREE0);
                         }
                     }
-                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE0);
-                    FA_TRACE_EV(0, 1);   // V and next K landed, S0 read by the softmax warps
+                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE0), (k - 1u) & 1u, BAR_OFREE0);
                     // tile 0
                     if (more) {
                         tc_fence_after();
                         if (leader && ok) {
                             issue_qk<H>(tS0, sQ, slot_addr(tk));
                             tc_commit(bar(BAR_S0));
-                            // the Q K^T of an item's last key step is its last use of the query tile
-                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY0));
+                            if (next_last_of_seg) tc_commit(bar(BAR_QEMPTY0));
                         }
                     }
-                    FA_TRACE_EV(0, 4);   // next Q K^T of tile 0 issued
-                    mwait(bar(BAR_P0), g & 1u, ctl, kRoleMma | BAR_P0);
-                    FA_TRACE_EV(0, 2);   // P0 ready
+                    mwait(bar(BAR_P0), g & 1u, BAR_P0);
                     tc_fence_after();
                     if (more) mbar_poll_begin<3>(bar(BAR_SFREE1), g & 1u);   // read behind the P V below
                     if (leader && ok) {
                         issue_pv<H>(tO0, tP0, slot_addr(tv), acc);
                         tc_commit(bar(BAR_PV0));
                     }
-                    FA_TRACE_EV(0, 8);   // P V of tile 0 issued
                     // tile 1
-                    if (more && next_new_item) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, ctl, kRoleMma | BAR_QFULL1);
-                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, ctl, kRoleMma | BAR_OFREE1);
+                    if (more && next_new_seg) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, BAR_QFULL1);
+                    if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, BAR_OFREE1);
                     if (more) {
-                        if (!mbar_poll_end<3>()) mwait(bar(BAR_SFREE1), g & 1u, ctl, kRoleMma | BAR_SFREE1);
-                        FA_TRACE_EV(0, 12);  // S1 read by the softmax warps
+                        if (!mbar_poll_end<3>()) mwait(bar(BAR_SFREE1), g & 1u, BAR_SFREE1);
                         tc_fence_after();
                         if (leader && ok) {
                             issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
                             tc_commit(bar(BAR_S1));
-                            if (next_new_item ? n == 1 : j + 2 == n) tc_commit(bar(BAR_QEMPTY1));
+                            if (next_last_of_seg) tc_commit(bar(BAR_QEMPTY1));
                             free_slot(tk);
                         }
                     }
-                    FA_TRACE_EV(0, 7);   // next Q K^T of tile 1 issued
-                    mwait(bar(BAR_P1), g & 1u, ctl, kRoleMma | BAR_P1);
-                    FA_TRACE_EV(0, 5);   // P1 ready
+                    mwait(bar(BAR_P1), g & 1u, BAR_P1);
                     tc_fence_after();
                     // what the next step starts with: test now, read at the top of the next step
                     polled = more;
@@ -998,30 +1457,30 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         tc_commit(bar(BAR_PV1));
                         free_slot(tv);
                     }
-                    FA_TRACE_EV(0, 10);  // P V of tile 1 issued
-                    if (++j == n) { j = 0; ++k; }
+                    if (++j == len) { j = 0; ++k; len = seg_len(pl, p, k); }
                 }
             }
-            const int bar_final = warp == 12 ? BAR_FINAL : BAR_FINAL2;
             // Every MMA this warp issued has to retire before the CTA releases tensor memory and shared
             // memory, whether or not a wait gave up on the way: this wait does not look at the abort flag.
+            const int bar_final = warp == 12 ? BAR_FINAL : BAR_FINAL2;
             if (leader) tc_commit(bar(bar_final));
             __syncwarp();
             mbar_wait_certain(bar(bar_final), 0, ctl, kRoleMma | static_cast<uint32_t>(bar_final));
         } else if (warp == 13 && elect_one()) {
             // -------------------------------------------------------------- TMA producer
             uint32_t t = 0;           // ring item
-            uint32_t k = 0;           // item count of this CTA
+            uint32_t k = 0;           // segment
             bool stop = false;
             bool q_pending[2] = {false, false};
-            for (uint32_t item = blockIdx.x; item < n_items && !stop; item += gridDim.x, ++k) {
-                const uint32_t q_pair = item % q_pairs, bh = item / q_pairs;
+            for (; k < nseg && !stop; ++k) {
+                const Seg sg = get_seg(pl_s, t0, p, k);
+                const uint32_t q_pair = sg.item % q_pairs, bh = sg.item / q_pairs;
                 const int32_t col0 = static_cast<int32_t>((bh % p.R) * H);
                 const int32_t batch = static_cast<int32_t>(bh / p.R);
                 const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
-                for (uint32_t tt = 0; tt < 2 * n; ++tt, ++t) {
+                for (uint32_t tt = 0; tt < 2 * sg.len; ++tt, ++t) {
                     if (tt < 2) {
-                        // query tile tt of this item, once the previous item has let go of the buffer
+                        // query tile tt of this segment, once the previous one has let go of the buffer
                         if (k > 0 && !mbar_wait(bar(BAR_QEMPTY0 + tt), (k - 1u) & 1u, ctl,
                                                 kRoleProducer | (BAR_QEMPTY0 + tt))) { stop = true; break; }
                         load_tile<H>(sQ + tt * G::kTileBytes, &tmQ, bar(BAR_QFULL0 + tt), col0,
@@ -1032,7 +1491,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (!mbar_wait(bar(BAR_EMPTY + slot), ((t / NS) & 1u) ^ 1u, ctl,
                                    kRoleProducer | (BAR_EMPTY + slot))) { stop = true; break; }
                     load_tile<H>(sRing + slot * G::kTileBytes, (tt & 1u) ? &tmV : &tmK, bar(BAR_FULL + slot),
-                                 col0, static_cast<int32_t>((tt >> 1) * kTile), batch);
+                                 col0, static_cast<int32_t>((sg.j0 + (tt >> 1)) * kTile), batch);
                 }
             }
             if (abort_flag != 0u) {
@@ -1056,8 +1515,11 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     tc_fence_before();
     __syncthreads();
-#if defined(FA_TRACE) || defined(FA_CYCLES)
-    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7 * 512 + 1] = static_cast<unsigned long long>(clock64());
+#ifdef FA_CYCLES
+    if (p.cycles != nullptr && blockIdx.x == 0 && tid == 0) {
+        p.cycles[4 * (p.launch_id & 63u) + 2] = global_timer_ns();
+        p.cycles[4 * (p.launch_id & 63u) + 3] = static_cast<unsigned long long>(clock64() - cyc0);
+    }
 #endif
     if (warp == 12) {
         tc_fence_after();

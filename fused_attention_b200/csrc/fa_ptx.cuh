@@ -199,6 +199,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint3
         : "memory");
 }
 
+// Ask for a tile to be brought into L2 (nothing is returned to the SM and nothing signals completion).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* map, int32_t x, int32_t y, int32_t z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+
 // 3-D tiled store shared -> global as one bulk group; the box is clipped at the tensor's bounds.
 // Coordinates must not be negative; x * sizeof(element) must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int32_t x, int32_t y, int32_t z) {
@@ -214,6 +222,14 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // make generic-proxy writes to shared memory visible to the async proxy (TMA)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
 
 // ----------------------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
@@ -375,6 +391,20 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     uint64_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
+}
+
+// Load with acquire semantics at device scope: loads that follow it in program order see what the
+// writer of the value had made visible (with a release or a fence) before writing it.
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* ptr) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 template <int kRegs>

@@ -57,12 +57,14 @@ enum {
     FA_B200_FLAG_NO_SPLIT = 16u        /* never divide the key axis of one (batch, head, query rows)
                                           problem among several CTAs.  By default the warp-specialised
                                           kernel may do so to keep every SM busy when the work items
-                                          do not fill a whole number of rounds; the partial results
+                                          leave most SMs idle in the last round; the partial results
                                           are merged in fp32, in a fixed order, so a call repeats bit
                                           for bit, but where the cuts fall depends on how many
-                                          (batch, head) pairs the call holds.  With this flag the bits
-                                          of one (batch, head) do not depend on what else is in the
-                                          call (a shard reproduces the undivided job exactly)       */
+                                          (batch, head) pairs the call holds, and a divided problem
+                                          differs from the undivided one by the kernel's ordinary
+                                          rounding error.  With this flag the bits of one
+                                          (batch, head) do not depend on what else is in the call (a
+                                          shard reproduces the undivided job exactly)                */
 };
 
 /*
@@ -176,6 +178,21 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]);
  */
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
                           int has_mask, uint32_t flags);
+
+/*
+ * How the warp-specialised kernel would spread a call's work over its CTAs on a device with
+ * `sm_count` SMs: out[0] = kernel (1 or 2, as fa_b200_select_kernel), out[1] = CTAs launched,
+ * out[2] = rounds of whole work items (a work item is 256 query rows of one (batch, head) against
+ * all keys; CTA c takes items c, c + out[1], ...), out[3] = work items of the last, partial round
+ * whose key steps are divided evenly among the first out[6] CTAs (0 = nothing is divided; a range
+ * is at least half a work item, so a work item has at most three parts), out[4] = key steps of
+ * those items in all, out[5] = key steps (tiles of 128 keys) per work item.  Pure arithmetic, no
+ * CUDA call; it is what the launcher itself uses (FA_B200_FLAG_NO_SPLIT in `flags` is honoured).
+ * No counterpart in the reference, whose grid is one CTA per (batch, query chunk, head)
+ * (include/fused_attn.cuh:883).
+ */
+int fa_b200_describe_schedule(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
+                              uint32_t flags, uint32_t sm_count, uint32_t out[7]);
 
 #ifdef __cplusplus
 }

@@ -80,7 +80,6 @@ def test_argument_rejections_happen_before_any_cuda_call(lib):
     assert _call(lib, flags=_lib.FLAG_NO_OVERLAP | 3) == _lib.ERR_FLAGS
     assert _call(lib, B=0, flags=_lib.FLAG_NO_OVERLAP) == _lib.ERR_SHAPE   # the bit itself is known
     assert _call(lib, H=32, flags=_lib.FLAG_FORCE_PIPELINED) == _lib.ERR_FLAGS
-    assert _call(lib, H=64, F=64, mask=_aligned(), flags=_lib.FLAG_FORCE_PIPELINED) == _lib.ERR_FLAGS
 
 
 def test_host_entry_rejections(lib):
@@ -101,7 +100,8 @@ def test_kernel_selection(lib):
     assert sel(1, 2048, 512, 128, 0, 0) == 2       # 32 items only, but 16 key steps each: pipelined
     assert sel(1, 512, 512, 128, 0, 0) == 1        # 8 items of 4 key steps cannot occupy the SMs
     assert sel(4, 2048, 512, 16, 0, 0) == 1        # small head_dim
-    assert sel(4, 2048, 4096, 128, 1, 0) == 1      # mask
+    assert sel(4, 2048, 4096, 128, 1, 0) == 2      # a mask does not change the choice
+    assert sel(4, 2048, 512, 32, 1, 0) == 1
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_FORCE_SIMPLE) == 1
     assert sel(1, 256, 256, 64, 0, _lib.FLAG_FORCE_PIPELINED) == 2
     assert sel(1, 256, 250, 64, 0, 0) == _lib.ERR_SHAPE

@@ -89,3 +89,56 @@ def test_inputs_are_seeded_and_sliced_consistently():
     full = workload_inputs(w)
     part = workload_inputs(w, heads=slice(1, 3))
     assert torch.equal(part[1], full[1][:, :, 64:192])
+
+
+@pytest.mark.parametrize("B,R,L,H", [(4, 32, 2048, 128), (4, 16, 2048, 128), (4, 8, 2048, 128), (4, 4, 2048, 128),
+                                     (8, 12, 512, 64), (64, 16, 197, 64), (1, 32, 16384, 128), (1, 4, 16384, 128),
+                                     (2, 3, 818, 128), (1, 4, 2048, 128), (1, 2, 4096, 64), (5, 7, 700, 64),
+                                     (1, 1, 100000, 128), (3, 50, 1000, 128), (2, 2, 700, 128)])
+@pytest.mark.parametrize("sms", [148, 132, 16])
+def test_every_key_step_of_every_work_item_is_scheduled_exactly_once(B, R, L, H, sms):
+    """The kernel's schedule (whole items round-robin, a divided last round) restated in Python from
+    what the launcher reports: full coverage, no overlap, and the limits the kernel relies on."""
+    sched = fa.describe_schedule(B, L, R * H, H, flags=fa._lib.FLAG_FORCE_PIPELINED, sm_count=sms)
+    n = sched["key_steps"]
+    assert n == -(-L // 128)
+    n_items = -(-L // 256) * R * B
+    grid, T = sched["grid"], sched["tail_steps"]
+    assert 1 <= grid <= sms
+    seen = {}
+    for cta in range(grid):
+        segs = fa.cta_segments(sched, n_items, cta)
+        tail = [s for s in segs if s[2] != n or s[0] >= sched["full_rounds"] * grid] if T else []
+        assert len(tail) <= 2                                  # two scratch slots per CTA
+        for item, j0, ln in segs:
+            assert 0 <= item < n_items and ln >= 1 and j0 + ln <= n
+            for j in range(j0, j0 + ln):
+                assert (item, j) not in seen
+                seen[(item, j)] = cta
+    assert len(seen) == n_items * n
+    if T:
+        tg = sched["tail_grid"]
+        assert T == sched["tail_items"] * n and 1 <= tg <= grid and T * tg < 2 ** 32
+        assert sched["full_rounds"] * sms + sched["tail_items"] == n_items
+        assert sched["full_rounds"] == 0 or grid == sms
+        busiest = max(sum(s[2] for s in fa.cta_segments(sched, n_items, c)) for c in range(grid))
+        whole_rounds = -(-n_items // sms) * n
+        assert busiest < whole_rounds - 5 - max(1, whole_rounds // 20)    # only where it clearly pays (see the launcher)
+        for item in range(sched["full_rounds"] * grid, n_items):
+            ctas = sorted({seen[(item, j)] for j in range(n)})
+            assert len(ctas) <= 3 and ctas == list(range(ctas[0], ctas[-1] + 1))   # consecutive CTAs, at most 3 parts
+    # undivided on request
+    whole = fa.describe_schedule(B, L, R * H, H, flags=fa._lib.FLAG_FORCE_PIPELINED | fa._lib.FLAG_NO_SPLIT, sm_count=sms)
+    assert whole["tail_steps"] == 0 and whole["grid"] == min(sms, n_items)
+
+
+def test_headline_shards_are_divided_as_designed():
+    d = lambda R: fa.describe_schedule(4, 2048, R * 128, 128)
+    assert d(32)["tail_steps"] == 0                       # 6.92 rounds: the last one is nearly full
+    # the shards of the headline job are not divided: what it would save (8, 4, 2 key steps at 2, 4, 8 GPUs) is
+    # about what it costs
+    assert d(16)["tail_steps"] == 0 and d(8)["tail_steps"] == 0 and d(4)["tail_steps"] == 0
+    few = fa.describe_schedule(1, 2048, 4 * 128, 128)     # 32 items on 148 SMs: two CTAs per item
+    assert (few["grid"], few["full_rounds"], few["tail_items"], few["tail_grid"]) == (64, 0, 32, 64)
+    long = fa.describe_schedule(1, 16384, 4 * 128, 128)   # 256 items of 128 key steps: the last 108 are divided
+    assert (long["full_rounds"], long["tail_items"], long["tail_grid"]) == (1, 108, 148)

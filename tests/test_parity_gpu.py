@@ -20,7 +20,7 @@ from oracle.naive_attention import MAX_ABS_TOL, MEAN_ABS_TOL, attention as oracl
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
-SIMPLE, PIPE = _lib.FLAG_FORCE_SIMPLE, _lib.FLAG_FORCE_PIPELINED
+SIMPLE, PIPE, WHOLE = _lib.FLAG_FORCE_SIMPLE, _lib.FLAG_FORCE_PIPELINED, _lib.FLAG_NO_SPLIT
 
 
 def run(q, k, v, H, mask=None, flags=0, chunk=None):
@@ -210,10 +210,15 @@ def test_tensors_larger_than_four_gib(flags):
     for t in (q, k, v):
         for b in range(B):                     # filled entry by entry: no fp32 temporary of the whole tensor
             t[b] = torch.randn(L, F, generator=g, device="cuda", dtype=torch.float16)
-    y = fa.attention_forward(H, 32 if H == 128 else 16, q, k, v, flags=flags)
+    y = fa.attention_forward(H, 32 if H == 128 else 16, q, k, v, flags=flags | WHOLE)
     for b in (0, 8, B - 1):
-        alone = fa.attention_forward(H, 32 if H == 128 else 16, q[b:b + 1], k[b:b + 1], v[b:b + 1], flags=flags)
+        alone = fa.attention_forward(H, 32 if H == 128 else 16, q[b:b + 1], k[b:b + 1], v[b:b + 1], flags=flags | WHOLE)
         assert torch.equal(y[b], alone[0]), b
+    # the default schedule may divide the key axis of the last work items of a call among CTAs: same values up
+    # to the kernel's ordinary rounding error
+    y_div = fa.attention_forward(H, 32 if H == 128 else 16, q, k, v, flags=flags)
+    assert float((y_div[B - 1].float() - y[B - 1].float()).abs().max()) <= MAX_ABS_TOL / 4
+    y = y_div
     b = B - 1
     for h in (0, R // 2, R - 1):               # heads at both ends of the last entry against fp32 attention
         qf, kf, vf = (t[b, :, h * H:(h + 1) * H].float() for t in (q, k, v))
@@ -233,6 +238,80 @@ def test_persistent_kernel_with_several_items_per_cta(B, R, L, H):
     q, k, v = make_inputs(B, L, R * H, 1.0, 2000 + L)
     expected = oracle(q, k, v, H)
     assert_close(run(q, k, v, H, flags=PIPE), expected)
+
+
+def _device_fp32(q, k, v, H):
+    B, L, F = q.shape
+    qf, kf, vf = (t.float().view(B, L, F // H, H).transpose(1, 2) for t in (q, k, v))
+    return (torch.softmax(qf @ kf.mT / H ** 0.5, -1) @ vf).transpose(1, 2).reshape(B, L, F)
+
+
+@pytest.mark.parametrize("B,R,L,H", [(1, 4, 2048, 128), (1, 2, 5000, 64), (1, 1, 4096, 128), (1, 3, 16384 + 77, 128),
+                                     (1, 40, 3000, 64), (2, 5, 2000, 64), (1, 4, 16384, 128), (1, 16, 8192, 128),
+                                     (1, 8, 8192, 64), (1, 3, 2300, 64), (1, 6, 3000, 128), (1, 7, 2500, 128)])
+def test_last_round_divided_among_ctas(B, R, L, H):
+    """Shapes whose work items do not fill a whole number of rounds of the persistent kernel: the key axis
+    of the last round's items is divided among CTAs and the parts are merged in fp32.  Against fp32
+    attention on the same GPU, against the same call with whole items, and twice for the bits."""
+    sched = fa.describe_schedule(B, L, R * H, H, sm_count=fa.query(0)["sm_count"])
+    assert sched["kernel"] == "pipelined" and sched["tail_steps"] > 0, sched
+    g = torch.Generator(device="cuda")
+    g.manual_seed(L + R)
+    q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() for _ in range(3))
+    y = fa.attention_forward(H, 32, q, k, v, flags=_lib.FLAG_SYNC)
+    y2 = fa.attention_forward(H, 32, q, k, v, flags=_lib.FLAG_SYNC)
+    y_whole = fa.attention_forward(H, 32, q, k, v, flags=WHOLE | _lib.FLAG_SYNC)
+    assert torch.equal(y, y2)                                   # the merge order is fixed: no run-to-run noise
+    ref = _device_fp32(q, k, v, H)
+    d = (y.float() - ref).abs()
+    assert torch.isfinite(y).all()
+    assert float(d.max()) <= MAX_ABS_TOL and float(d.mean()) <= MEAN_ABS_TOL, (float(d.max()), float(d.mean()))
+    # Against the undivided schedule: every part takes its exponentials against its own reference maximum, so
+    # the fp16 roundings of P differ between the two schedules; the results differ by the kernel's ordinary
+    # rounding error (observed up to 1e-4), a fraction of the bound against the oracle.
+    assert float((y.float() - y_whole.float()).abs().max()) <= MAX_ABS_TOL / 4
+
+
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("pattern", ["rising", "falling", "spike"])
+def test_divided_items_whose_parts_have_far_apart_maxima(H, pattern):
+    """The parts of a divided item each keep their own reference maximum; here the maxima of the parts lie
+    hundreds of powers of two apart (rising or falling score levels along the keys, or one late spike), so
+    the weights of the merge range from 1 down to 0."""
+    B, R, L = 1, 4, 128 * 16 + 50
+    assert fa.describe_schedule(B, L, R * H, H, sm_count=fa.query(0)["sm_count"])["tail_steps"] > 0
+    q, k, v = make_inputs(B, L, R * H, 1.0, 4100 + H)
+    q = (q.float() * 0.05 + 1.0).half()
+    tile = torch.arange(L) // 128
+    if pattern == "rising":
+        level = 40.0 * tile
+    elif pattern == "falling":
+        level = 40.0 * (tile.max() - tile)
+    else:
+        level = torch.zeros(L); level[128 * 11 + 77] = 400.0
+    k = (k.float() * 0.05 + (level / H)[None, :, None]).half()
+    expected = oracle(q, k, v, H)
+    y = run(q, k, v, H)
+    assert torch.isfinite(y).all()
+    assert_close(y, expected)
+    assert_close(run(q, k, v, H, flags=WHOLE), expected)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_a_shard_reproduces_the_bits_of_the_undivided_job(world):
+    """Strong scaling by head: with FA_B200_FLAG_NO_SPLIT the heads of a shard have the bits they have in the
+    one-GPU job (each (batch, head) is computed the same way whatever else is in the call); the default
+    schedule, which may divide the key axis of some work items, stays within the kernel's rounding error of it."""
+    w = WORKLOADS["llama7b_prefill"]
+    q, k, v = (t.cuda() for t in workload_inputs(w))
+    y_full = fa.attention_forward(w.H, 128, q, k, v, flags=WHOLE)
+    for rank in (0, world - 1):
+        sh = fa.shard_units(w.B, w.R, world, rank)
+        sq, sk, sv = (fa.slice_tensor(t, sh, w.H) for t in (q, k, v))
+        want = y_full[sh.b0:sh.b1, :, sh.h0 * w.H:sh.h1 * w.H]
+        assert torch.equal(fa.attention_forward(w.H, 128, sq, sk, sv, flags=WHOLE), want)
+        got = fa.attention_forward(w.H, 128, sq, sk, sv).float()
+        assert float((got - want.float()).abs().max()) <= MAX_ABS_TOL / 4
 
 
 def test_large_logits_stay_finite():
@@ -321,7 +400,8 @@ def test_additive_mask(H, L):
     mask[1, :, L - L // 3:] = float("-inf")                                        # padding
     mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(1)).half()
     expected = oracle(q, k, v, H, mask)
-    assert_close(run(q, k, v, H, mask=mask), expected)
+    for flags in kernels_for(H):
+        assert_close(run(q, k, v, H, mask=mask, flags=flags), expected)
 
 
 @pytest.mark.parametrize("L", [127, 200, 256, 1000])
@@ -334,14 +414,16 @@ def test_additive_mask_rows_at_any_alignment(L):
     mask = (0.5 * torch.randn(2, L, L, generator=gen)).half()
     mask[0] += torch.triu(torch.full((L, L), float("-inf")), diagonal=1).half()
     expected = oracle(q, k, v, H, mask)
-    assert_close(run(q, k, v, H, mask=mask), expected)
+    for flags in (SIMPLE, PIPE):
+        assert_close(run(q, k, v, H, mask=mask, flags=flags), expected)
     # the same values in a buffer whose first element is 2 bytes past a 16-byte boundary
     store = torch.empty(mask.numel() + 8, dtype=torch.float16, device="cuda")
     shifted = store[1:1 + mask.numel()].view_as(mask)
     shifted.copy_(mask)
     assert shifted.data_ptr() % 16 == 2
-    y = fa.attention_forward(H, 16, q.cuda(), k.cuda(), v.cuda(), shifted, flags=_lib.FLAG_SYNC)
-    assert_close(y.float().cpu(), expected)
+    for flags in (SIMPLE, PIPE):
+        y = fa.attention_forward(H, 16, q.cuda(), k.cuda(), v.cuda(), shifted, flags=flags | _lib.FLAG_SYNC)
+        assert_close(y.float().cpu(), expected)
 
 
 def test_value_of_ones_gives_ones_at_full_size():
@@ -374,6 +456,9 @@ def test_key_permutation_invariance_at_full_size():
 
 
 def test_host_buffer_entry_point_matches_device_entry_point():
+    """The host entry point cuts the call into chunks and runs every chunk with whole work items, so it
+    gives the bits of a device-pointer call with FA_B200_FLAG_NO_SPLIT."""
+    run = lambda *a, **kw: globals()["run"](*a, flags=WHOLE, **kw)
     q, k, v = make_inputs(2, 300, 256, 1.0, 21)
     y_dev = run(q, k, v, 128)
     y_host = fa.attention_forward_host(128, 128, q.pin_memory(), k.pin_memory(), v.pin_memory()).float()
@@ -407,7 +492,8 @@ def test_concurrent_callers_from_several_threads():
     (which share per-device staging buffers and must serialise themselves) from four threads."""
     import threading
     q, k, v = make_inputs(2, 700, 256, 1.0, 91)
-    expected = run(q, k, v, 128)
+    expected = run(q, k, v, 128)                  # divided schedule, as the device workers below
+    expected_whole = run(q, k, v, 128, flags=WHOLE)   # what the host entry point reproduces
     dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
     results, errors = {}, []
 
@@ -438,7 +524,7 @@ def test_concurrent_callers_from_several_threads():
         t.join()
     assert not errors, errors
     for idx in range(4):
-        assert torch.equal(results[idx], expected)
+        assert torch.equal(results[idx], expected if idx < 2 else expected_whole)
 
 
 def test_non_default_stream_and_output_placement():
@@ -603,7 +689,7 @@ def test_mask_against_the_reference_kernel_single_chunk(H, C):
     y_ref = _run_ref_wmma(lib, q, k, v, H, C, dmask)
     err_ref = error_metrics(y_ref.float().cpu(), expected)
     assert err_ref["max_abs"] <= 1e-2, err_ref       # the reference kernel and the oracle formula mean the same mask
-    for flags in (0, SIMPLE):
+    for flags in kernels_for(H):
         y = fa.attention_forward(H, C, q, k, v, dmask, flags=flags | _lib.FLAG_SYNC)
         torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
         assert_close(y.float().cpu(), expected)
