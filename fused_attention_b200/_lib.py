@@ -44,6 +44,8 @@ FLAG_FORCE_PIPELINED = 2
 FLAG_SYNC = 4
 FLAG_NO_OVERLAP = 8
 FLAG_NO_SPLIT = 16
+FLAG_FORCE_PAIR = 32
+FLAG_NO_PAIR = 64
 
 _lock = threading.Lock()
 _lib = None

@@ -17,6 +17,7 @@
 
 #include "fa_b200.h"
 #include "fa_kernels.cuh"
+#include "fa_pair.cuh"
 
 namespace {
 
@@ -45,6 +46,7 @@ struct DeviceCtx {
     int cc_major = 0, cc_minor = 0, sm_count = 0, smem_optin = 0;
     uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count, id of the launch that reported, -}
     std::atomic<uint32_t> attr_done{0};   // bit per kernel instance whose smem attribute is set
+    std::atomic<int> pair_clusters{-1};    // how many CTA pairs of fa_fwd_pair the device holds at once (-1: not asked yet)
     // Scratch of launches that divide their last round of work items (fa::Plan): one buffer per stream,
     // because launches on different streams may run at the same time.  kSplitPool buffers are allocated
     // with the context; a launch on a stream that finds none free runs undivided.
@@ -182,8 +184,11 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
     if (all & 15u) return FA_B200_ERR_ALIGNMENT;
     if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return FA_B200_ERR_ALIGNMENT;
     const uint32_t known = FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_SYNC |
-                           FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT;
+                           FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR | FA_B200_FLAG_NO_PAIR;
     if (flags & ~known) return FA_B200_ERR_FLAGS;
+    if (flags & FA_B200_FLAG_FORCE_PAIR) {
+        if (H != 128 || mask || (flags & (FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_NO_PAIR))) return FA_B200_ERR_FLAGS;
+    }
     if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && H < 64) return FA_B200_ERR_FLAGS;
     return FA_B200_OK;
@@ -193,7 +198,7 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
 int select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t H, bool has_mask, uint32_t flags,
                   int sm_count) {
     if (flags & FA_B200_FLAG_FORCE_SIMPLE) return 1;
-    if (flags & FA_B200_FLAG_FORCE_PIPELINED) return 2;
+    if (flags & (FA_B200_FLAG_FORCE_PIPELINED | FA_B200_FLAG_FORCE_PAIR)) return 2;
     (void)has_mask;   // both kernels take the additive mask
     if (H < 64) return 1;
     // The pipelined kernel works on items of two query tiles (256 rows) on persistent CTAs.  It wins
@@ -326,6 +331,63 @@ const SplitScratch* scratch_for_stream(DeviceCtx& c, cudaStream_t st) {
     return nullptr;
 }
 
+// When the kernel on pairs of CTAs is taken: head_dim 128, no mask, whole work items, and on request only
+// (FA_B200_FLAG_FORCE_PAIR) until it has been measured against the other one.
+bool use_pair_kernel(uint32_t H, bool has_mask, const Schedule& sch, const Params& p, uint32_t flags) {
+    (void)p;
+    if (H != 128 || has_mask || (flags & FA_B200_FLAG_NO_PAIR)) return false;
+    if (flags & FA_B200_FLAG_FORCE_PAIR) return true;
+    (void)sch;
+    return false;
+}
+
+// The pair kernel: clusters of two CTAs, as many as the device holds at once (asked once per device).
+int launch_pair(DeviceCtx& c, const CUtensorMap& mq, const CUtensorMap& mkh, const CUtensorMap& mv,
+                const CUtensorMap& my, const Params& p, uint32_t n_quad_items, cudaStream_t st, bool overlap,
+                bool* launched) {
+    constexpr int smem = fa::PairCfg::kSmemBytes;
+    constexpr int slot = 12;
+    auto kern = fa::fa_fwd_pair;
+    *launched = false;
+    if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        c.attr_done.fetch_or(1u << slot, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(512, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    int clusters = c.pair_clusters.load(std::memory_order_acquire);
+    if (clusters < 0) {
+        cfg.gridDim = dim3(static_cast<unsigned>(c.sm_count) & ~1u, 1, 1);
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        if (n > c.sm_count / 2) n = c.sm_count / 2;
+        c.pair_clusters.store(n, std::memory_order_release);
+        clusters = n;
+    }
+    if (clusters <= 0) return FA_B200_OK;   // the device cannot hold a pair: the caller takes the other kernel
+    const uint32_t nc = n_quad_items < static_cast<uint32_t>(clusters) ? n_quad_items : static_cast<uint32_t>(clusters);
+    cfg.gridDim = dim3(2 * nc, 1, 1);
+    cfg.numAttrs = overlap ? 2u : 1u;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mq, mkh, mv, my, p);
+    *launched = true;
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 // Device-pointer launch on `st`.  Caller holds no lock.
 int forward_device(const void* q, const void* k, const void* v, const void* mask, void* y, uint32_t B,
                    uint32_t L, uint32_t F, uint32_t H, int device, cudaStream_t st, uint32_t flags) {
@@ -394,7 +456,19 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                     // Y as a TMA store target: boxes of 32 rows x 64 columns (one epilogue warp each)
                     CUtensorMap my;
                     rc = make_map(&my, y, B, L, F, H, 32);
-                    if (rc == FA_B200_OK) {
+                    bool done = false;
+                    if (rc == FA_B200_OK && use_pair_kernel(H, mask != nullptr, sch, p, flags)) {
+                        // K as halves of a tile: boxes of 64 keys x 64 columns
+                        CUtensorMap mkh;
+                        rc = make_map(&mkh, k, B, L, F, H, 64);
+                        if (rc == FA_B200_OK) {
+                            Params pp = p;
+                            pp.full_rounds = pp.tail_items = pp.tail_steps = pp.tail_grid = 0;
+                            const uint32_t quads = ((p.q_pairs + 1u) / 2u) * p.R * B;
+                            rc = launch_pair(*c, mq, mkh, mv, my, pp, quads, st, overlap, &done);
+                        }
+                    }
+                    if (rc == FA_B200_OK && !done) {
                         if (mask)
                             rc = H == 128 ? launch_pipelined<128, true>(*c, 10, mq, mk, mv, my, p, sch.grid, st, overlap)
                                           : launch_pipelined<64, true>(*c, 11, mq, mk, mv, my, p, sch.grid, st, overlap);

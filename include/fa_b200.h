@@ -54,6 +54,10 @@ enum {
                                           while the previous kernel of the stream drains; they touch
                                           global memory only once that kernel has completed, so the
                                           stream's ordering guarantees are unchanged             */
+    FA_B200_FLAG_FORCE_PAIR = 32u,     /* head_dim 128, no mask: always use the kernel that runs on pairs
+                                          of CTAs (one MMA of 256 rows for two SMs); implies whole work
+                                          items                                                     */
+    FA_B200_FLAG_NO_PAIR = 64u,        /* never use that kernel                                      */
     FA_B200_FLAG_NO_SPLIT = 16u        /* never divide the key axis of one (batch, head, query rows)
                                           problem among several CTAs.  By default the warp-specialised
                                           kernel may do so to keep every SM busy when the work items

@@ -80,6 +80,9 @@ def test_argument_rejections_happen_before_any_cuda_call(lib):
     assert _call(lib, flags=_lib.FLAG_NO_OVERLAP | 3) == _lib.ERR_FLAGS
     assert _call(lib, B=0, flags=_lib.FLAG_NO_OVERLAP) == _lib.ERR_SHAPE   # the bit itself is known
     assert _call(lib, H=32, flags=_lib.FLAG_FORCE_PIPELINED) == _lib.ERR_FLAGS
+    assert _call(lib, H=64, F=64, flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS              # head_dim 128 only
+    assert _call(lib, H=128, F=128, flags=_lib.FLAG_FORCE_PAIR | _lib.FLAG_NO_PAIR) == _lib.ERR_FLAGS
+    assert _call(lib, H=128, F=128, mask=_aligned(), flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS
 
 
 def test_host_entry_rejections(lib):

@@ -21,6 +21,8 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
 SIMPLE, PIPE, WHOLE = _lib.FLAG_FORCE_SIMPLE, _lib.FLAG_FORCE_PIPELINED, _lib.FLAG_NO_SPLIT
+PAIR = _lib.FLAG_FORCE_PAIR                      # head_dim 128 on pairs of CTAs (one MMA of 256 rows for two SMs)
+ONE = PIPE | _lib.FLAG_NO_PAIR                   # the warp-specialised kernel on single CTAs
 
 
 def run(q, k, v, H, mask=None, flags=0, chunk=None):
@@ -45,7 +47,7 @@ def status_word_stays_clear():
 
 
 def kernels_for(H, L=1024):
-    return [0, SIMPLE] + ([PIPE] if H >= 64 else [])
+    return [0, SIMPLE] + ([ONE] if H >= 64 else []) + ([PAIR] if H == 128 else [])
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
@@ -93,7 +95,7 @@ def _fp32_attention_on_device(q, k, v, H, b, h):
 
 @pytest.mark.parametrize("name", ["llama7b_prefill", "long_context"])
 def test_full_size_configurations_every_row(name):
-    """Every query row of every (batch, head) of the two large configurations, both kernels, against
+    """Every query row of every (batch, head) of the two large configurations, all three kernels, against
     fp32 attention computed on the same GPU (the CPU oracle would need minutes to hours at these sizes);
     that checker is itself held against the CPU oracle on sampled rows of every head."""
     w = WORKLOADS[name]
@@ -102,9 +104,10 @@ def test_full_size_configurations_every_row(name):
     g = torch.Generator().manual_seed(w.seed + 1)
     rows = sorted(set(torch.randint(0, w.L, (24,), generator=g).tolist()) | {0, w.L - 1})
     cpu = oracle(hq, hk, hv, w.H, query_rows=rows)                 # [B, rows, F]
-    ys = {flags: fa.attention_forward(w.H, 128, q, k, v, flags=flags) for flags in (PIPE, SIMPLE)}
+    kernels = (ONE, PAIR, SIMPLE)
+    ys = {flags: fa.attention_forward(w.H, 128, q, k, v, flags=flags) for flags in kernels}
     torch.cuda.synchronize()
-    worst = {PIPE: [0.0, 0.0], SIMPLE: [0.0, 0.0]}
+    worst = {flags: [0.0, 0.0] for flags in kernels}
     checker_worst = 0.0
     for b in range(w.B):
         for h in range(w.R):
@@ -115,7 +118,7 @@ def test_full_size_configurations_every_row(name):
                 worst[flags][0] = max(worst[flags][0], float(d.max()))
                 worst[flags][1] = max(worst[flags][1], float(d.mean()))
     assert checker_worst <= 2e-5, checker_worst      # fp32 against fp32: only the order of summation differs
-    for flags in (PIPE, SIMPLE):
+    for flags in kernels:
         assert worst[flags][0] <= MAX_ABS_TOL and worst[flags][1] <= MEAN_ABS_TOL, (flags, worst[flags])
 
 
@@ -314,11 +317,28 @@ def test_a_shard_reproduces_the_bits_of_the_undivided_job(world):
         assert float((got - want.float()).abs().max()) <= MAX_ABS_TOL / 4
 
 
+@pytest.mark.parametrize("B,R,L", [(1, 1, 1), (1, 1, 128), (1, 2, 129), (2, 3, 511), (2, 3, 512), (2, 3, 513), (1, 2, 1000),
+                                   (20, 10, 300), (3, 50, 700), (4, 32, 2048), (1, 3, 5000), (1, 1, 16384 + 77)])
+def test_kernel_on_pairs_of_ctas(B, R, L):
+    """head_dim 128 on clusters of two CTAs: a pair works on 512 query rows and every MMA is one instruction
+    of 256 rows for both SMs.  Lengths around the 512-row and 128-key boundaries, more work items than
+    pairs of SMs, a single item.  Same arithmetic in the same order as the single-CTA kernel: same bits."""
+    H = 128
+    g = torch.Generator(device="cuda")
+    g.manual_seed(L + R)
+    q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() for _ in range(3))
+    y = fa.attention_forward(H, 128, q, k, v, flags=PAIR | _lib.FLAG_SYNC)
+    assert torch.isfinite(y).all()
+    d = (y.float() - _device_fp32(q, k, v, H)).abs()
+    assert float(d.max()) <= MAX_ABS_TOL and float(d.mean()) <= MEAN_ABS_TOL, (float(d.max()), float(d.mean()))
+    assert torch.equal(y, fa.attention_forward(H, 128, q, k, v, flags=ONE | WHOLE | _lib.FLAG_SYNC))
+
+
 def test_large_logits_stay_finite():
     # sigma 4 at H=128 gives scores of a few hundred before scaling: exercises the running max
     q, k, v = make_inputs(1, 512, 256, 4.0, 5)
     expected = oracle(q, k, v, 128)
-    for flags in (SIMPLE, PIPE):
+    for flags in (SIMPLE, ONE, PAIR):
         y = run(q, k, v, 128, flags=flags)
         assert torch.isfinite(y).all()
         m = error_metrics(y, expected)
@@ -350,7 +370,7 @@ def test_reference_maximum_moves_between_key_tiles(H, pattern):
         level = 70.0 * (torch.arange(L) // 32)
     k = (k.float() * 0.05 + (level / H)[None, :, None]).half()   # raw score of key j is about level[j]
     expected = oracle(q, k, v, H)
-    for flags in (SIMPLE, PIPE):
+    for flags in (SIMPLE, ONE) + ((PAIR,) if H == 128 else ()):
         y = run(q, k, v, H, flags=flags)
         assert torch.isfinite(y).all()
         assert_close(y, expected)
@@ -365,7 +385,7 @@ def test_kernels_agree_and_are_deterministic():
     assert float((a - c).abs().max()) <= 1e-3
 
 
-@pytest.mark.parametrize("H,L,flags", [(128, 700, PIPE), (64, 300, PIPE), (64, 100, SIMPLE), (32, 200, SIMPLE)])
+@pytest.mark.parametrize("H,L,flags", [(128, 700, ONE), (128, 700, PAIR), (64, 300, PIPE), (64, 100, SIMPLE), (32, 200, SIMPLE)])
 def test_overlapped_launches_keep_the_order_of_the_stream(H, L, flags):
     """By default a launch may become resident while the previous kernel of the stream drains.  A chain of
     launches in which each one reads what the one before wrote (Y of step i is V of step i + 1, with no
