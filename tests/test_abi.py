@@ -76,7 +76,7 @@ def test_argument_rejections_happen_before_any_cuda_call(lib):
     assert _call(lib, F=48, H=32) == _lib.ERR_SHAPE
     assert _call(lib, q=_aligned() + 2) == _lib.ERR_ALIGNMENT
     assert _call(lib, flags=3) == _lib.ERR_FLAGS               # both force bits
-    assert _call(lib, flags=64) == _lib.ERR_FLAGS              # unknown bit
+    assert _call(lib, flags=1024) == _lib.ERR_FLAGS            # unknown bit
     assert _call(lib, flags=_lib.FLAG_NO_OVERLAP | 3) == _lib.ERR_FLAGS
     assert _call(lib, B=0, flags=_lib.FLAG_NO_OVERLAP) == _lib.ERR_SHAPE   # the bit itself is known
     assert _call(lib, H=32, flags=_lib.FLAG_FORCE_PIPELINED) == _lib.ERR_FLAGS
