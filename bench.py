@@ -309,6 +309,35 @@ def other_workloads(torch, fa, dev, peaks: dict, skip: str) -> dict:
     return out
 
 
+def masked_run(torch, fa, dev, w, peaks: dict, unmasked_ms: float) -> dict:
+    """The same workload with an additive causal mask [B, L, L] (0 on and below the diagonal, -inf above), one
+    GPU: the mask costs B*L*L*2 bytes of reads on top of Q, K, V, Y, and no work is skipped (the operator's mask
+    is data, not a causal flag), so the FLOP count is the unmasked one."""
+    host = __import__("fused_attention_b200.workloads", fromlist=["workload_inputs"]).workload_inputs(w)
+    bufs, n, one = device_copies(torch, host, dev, 2 * L2_BYTES, max_copies=8)
+    mask = torch.triu(torch.full((w.L, w.L), float("-inf"), device=dev, dtype=torch.float16), diagonal=1)
+    mask = mask.unsqueeze(0).expand(w.B, w.L, w.L).contiguous()
+    chunk = 128 if w.H == 128 else 64
+    for i in range(3):
+        fa.attention_forward(w.H, chunk, *bufs[i % n], mask)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    steps = 50
+    e0.record()
+    for i in range(steps):
+        fa.attention_forward(w.H, chunk, *bufs[i % n], mask)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    mask_bytes = w.B * w.L * w.L * 2
+    t_tensor = w.flops / (float(peaks["bf16_tflops"]) * 1e12)
+    t_hbm = (w.bytes + mask_bytes) / (float(peaks["hbm_gbs"]) * 1e9)
+    return {"mask": "causal, additive fp16 [B, L, L]", "ms_per_launch": ms, "tflops": w.flops / (ms * 1e-3) / 1e12,
+            "algorithmic_bytes": w.bytes + mask_bytes, "algorithmic_gbs": (w.bytes + mask_bytes) / (ms * 1e-3) / 1e9,
+            "bound": "tensor" if t_tensor >= t_hbm else "hbm", "frac_of_bound": max(t_tensor, t_hbm) / (ms * 1e-3),
+            "time_over_unmasked": ms / unmasked_ms, "kernel": fa.select_kernel(w.B, w.L, w.F, w.H, has_mask=True)}
+
+
 def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | None:
     import dataclasses
 
@@ -448,9 +477,11 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
 
     out = None
     peaks, peak_kind = measured_peaks()
-    others = None
+    others = masked = None
     if rank == 0 and world == 1 and not args.no_other_workloads:
         others = other_workloads(torch, fa, dev, peaks, skip=w.name)
+        if w.B * w.L * w.L * 2 <= 4 << 30:
+            masked = masked_run(torch, fa, dev, w, peaks, main["my_ms_per_launch"])
     if rank == 0:
         peak = float(peaks["bf16_tflops"])
         peak_sus = float(peaks.get("bf16_tflops_sustained", 0.0)) or None
@@ -495,6 +526,8 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
             out[other_scaling["scaling"]] = other_scaling
         if others is not None:
             out["other_workloads"] = others
+        if masked is not None:
+            out["masked"] = masked
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             tf, dt, sample = cpu_naive_attention(w, 12.0, threads)

@@ -119,14 +119,14 @@ def select_kernel(B: int, L: int, F: int, head_dim: int, has_mask: bool = False,
     rc = _lib.load().fa_b200_select_kernel(B, L, F, head_dim, int(has_mask), flags)
     if rc < 0:
         _lib.check(rc)
-    return {1: "simple", 2: "pipelined"}[rc]
+    return {1: "simple", 2: "pipelined", 3: "pipelined on pairs of CTAs"}[rc]
 
 
 def describe_schedule(B: int, L: int, F: int, head_dim: int, flags: int = 0, sm_count: int = 148) -> dict:
     """How the warp-specialised kernel spreads a call over its CTAs (``fa_b200_describe_schedule``)."""
     o = (ctypes.c_uint32 * 7)()
     _lib.check(_lib.load().fa_b200_describe_schedule(B, L, F, head_dim, int(flags), int(sm_count), o))
-    return {"kernel": {1: "simple", 2: "pipelined"}[o[0]], "grid": o[1], "full_rounds": o[2],
+    return {"kernel": {1: "simple", 2: "pipelined", 3: "pipelined on pairs of CTAs"}[o[0]], "grid": o[1], "full_rounds": o[2],
             "tail_items": o[3], "tail_steps": o[4], "key_steps": o[5], "tail_grid": o[6]}
 
 

@@ -331,14 +331,16 @@ const SplitScratch* scratch_for_stream(DeviceCtx& c, cudaStream_t st) {
     return nullptr;
 }
 
-// When the kernel on pairs of CTAs is taken: head_dim 128, no mask, whole work items, and on request only
-// (FA_B200_FLAG_FORCE_PAIR) until it has been measured against the other one.
-bool use_pair_kernel(uint32_t H, bool has_mask, const Schedule& sch, const Params& p, uint32_t flags) {
-    (void)p;
+// When the kernel on pairs of CTAs is taken: head_dim 128, no mask, whole work items (a call whose last
+// round is divided stays on single CTAs), and a number of 256-row blocks per (batch, head) that is even or
+// large, since a pair works on 512 rows and an odd block leaves one CTA of a pair without work.  Measured on
+// the headline shape: the same SM clocks per launch as on single CTAs, but less shared-memory and L2 traffic,
+// so under the power cap the SMs clock 2 to 3 % higher.
+bool use_pair_kernel(uint32_t H, bool has_mask, uint32_t q_pairs, uint32_t tail_steps, uint32_t flags) {
     if (H != 128 || has_mask || (flags & FA_B200_FLAG_NO_PAIR)) return false;
     if (flags & FA_B200_FLAG_FORCE_PAIR) return true;
-    (void)sch;
-    return false;
+    if (tail_steps != 0) return false;
+    return (q_pairs % 2u) == 0u || q_pairs >= 16u;
 }
 
 // The pair kernel: clusters of two CTAs, as many as the device holds at once (asked once per device).
@@ -441,7 +443,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                     // belongs to this stream.  A stream that is being captured gets none (the recorded launch
                     // could later be replayed next to anything).
                     const SplitScratch* scratch = nullptr;
-                    if (!(flags & FA_B200_FLAG_NO_SPLIT)) scratch = scratch_for_stream(*c, st);
+                    if (!(flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR))) scratch = scratch_for_stream(*c, st);
                     const Schedule sch = make_schedule(p.n_items, p.n_kv_tiles, static_cast<uint32_t>(c->sm_count),
                                                        scratch != nullptr);
                     p.full_rounds = sch.full_rounds;
@@ -457,7 +459,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                     CUtensorMap my;
                     rc = make_map(&my, y, B, L, F, H, 32);
                     bool done = false;
-                    if (rc == FA_B200_OK && use_pair_kernel(H, mask != nullptr, sch, p, flags)) {
+                    if (rc == FA_B200_OK && use_pair_kernel(H, mask != nullptr, p.q_pairs, sch.tail_steps, flags)) {
                         // K as halves of a tile: boxes of 64 keys x 64 columns
                         CUtensorMap mkh;
                         rc = make_map(&mkh, k, B, L, F, H, 64);
@@ -915,7 +917,18 @@ int fa_b200_describe_schedule(uint32_t B, uint32_t L, uint32_t F, uint32_t head_
         out[2] = out[3] = out[4] = out[6] = 0;
         return FA_B200_OK;
     }
-    const Schedule s = make_schedule(n_items, n, sm_count, (flags & FA_B200_FLAG_NO_SPLIT) == 0);
+    const Schedule s = make_schedule(n_items, n, sm_count,
+                                     (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
+    const uint32_t q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
+    if (use_pair_kernel(head_dim, false, q_pairs, s.tail_steps, flags) && sm_count >= 2) {
+        // pairs of CTAs: work items of 512 query rows, one cluster of two CTAs per pair of SMs
+        const uint32_t quads = ((q_pairs + 1) / 2) * (F / head_dim) * B, clusters = quads < sm_count / 2 ? quads : sm_count / 2;
+        out[0] = 3;
+        out[1] = 2 * clusters;
+        out[2] = (quads + clusters - 1) / clusters;
+        out[3] = out[4] = out[6] = 0;
+        return FA_B200_OK;
+    }
     out[1] = s.grid;
     out[2] = s.full_rounds;
     out[3] = s.tail_items;
@@ -936,7 +949,12 @@ int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
         (void)cudaGetLastError();
         sms = 148;
     }
-    return select_kernel(B, L, F, head_dim, has_mask != 0, flags, sms);
+    const int which = select_kernel(B, L, F, head_dim, has_mask != 0, flags, sms);
+    if (which != 2) return which;
+    const uint32_t n = (L + fa::kTile - 1) / fa::kTile, q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
+    const Schedule s = make_schedule(q_pairs * (F / head_dim) * B, n, static_cast<uint32_t>(sms),
+                                     (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
+    return use_pair_kernel(head_dim, has_mask != 0, q_pairs, s.tail_steps, flags) ? 3 : 2;
 }
 
 }  // extern "C"

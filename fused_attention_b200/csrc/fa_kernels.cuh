@@ -296,12 +296,32 @@ __device__ __forceinline__ void mask_tail(float (&s)[kTile], int valid) {
         if (i >= valid) s[i] = -INFINITY;
 }
 
-// s[i] += mask[i] * to_score for the first `valid` keys of a tile.  With `vec` (the row starts on a
-// 16-byte boundary: L a multiple of 8) whole groups of eight mask values are read with one 16-byte
-// load; the ragged remainder and unaligned rows are read value by value.
+// s[i] += mask[i] * to_score for the first `valid` keys of a tile.  Every thread reads its own row of the
+// mask, so the lanes of a warp touch 32 different lines per load instruction whatever its width: the wider the
+// load, the fewer passes through the load unit.  `align` is the alignment in bytes that every row start of
+// this call is known to have (32, 16 or 2): whole groups of 16 (8) mask values are read with one 32-byte
+// (16-byte) load; the ragged remainder and unaligned rows are read value by value.
 __device__ __forceinline__ void add_mask_row(float (&s)[kTile], const __half* mrow, int valid, float to_score,
-                                             bool vec) {
-    if (vec) {
+                                             uint32_t align) {
+    if (align >= 32u) {
+#pragma unroll
+        for (int i0 = 0; i0 < kTile; i0 += 16) {
+            if (i0 + 16 <= valid) {
+                uint32_t w[8];
+                ldg_256(mrow + i0, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                    s[i0 + 2 * e] = fmaf(f.x, to_score, s[i0 + 2 * e]);
+                    s[i0 + 2 * e + 1] = fmaf(f.y, to_score, s[i0 + 2 * e + 1]);
+                }
+            } else {
+#pragma unroll
+                for (int i = i0; i < i0 + 16; ++i)
+                    if (i < valid) s[i] = fmaf(__half2float(mrow[i]), to_score, s[i]);
+            }
+        }
+    } else if (align >= 16u) {
 #pragma unroll
         for (int i0 = 0; i0 < kTile; i0 += 8) {
             if (i0 + 8 <= valid) {
@@ -324,6 +344,12 @@ __device__ __forceinline__ void add_mask_row(float (&s)[kTile], const __half* mr
         for (int i = 0; i < kTile; ++i)
             if (i < valid) s[i] = fmaf(__half2float(mrow[i]), to_score, s[i]);
     }
+}
+
+// What every mask row start of a call is aligned to: rows are L fp16 values apart from the base address.
+__device__ __forceinline__ uint32_t mask_row_alignment(const Params& p) {
+    const uint32_t bits = (p.L * 2u) | static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.mask));
+    return (bits & 31u) == 0u ? 32u : ((bits & 15u) == 0u ? 16u : 2u);
 }
 
 // ============================================================================ simple kernel
@@ -429,8 +455,7 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const __half* mrow = p.mask + (static_cast<size_t>(batch) * p.L + q_row) * p.L +
                                      static_cast<size_t>(j) * kTile;
                 const int valid = min(static_cast<int>(p.L - j * kTile), kTile);
-                add_mask_row(s, mrow, valid, p.mask_to_score,
-                             ((p.L & 7u) | (reinterpret_cast<uintptr_t>(p.mask) & 15u)) == 0u);
+                add_mask_row(s, mrow, valid, p.mask_to_score, mask_row_alignment(p));
             }
         }
         if ((j + 1) * kTile > p.L) mask_tail(s, static_cast<int>(p.L - j * kTile));
@@ -995,12 +1020,12 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             l = 0.f;
             // with a mask: the row of mask[batch] this thread adds to its scores
             const __half* mask_row = nullptr;
-            bool mask_vec = false;
+            uint32_t mask_vec = 2;
             if constexpr (kHasMask) {
                 const uint32_t q_row = ((sg.item % q_pairs) * 2u + i) * kTile + row;
                 const uint32_t batch = (sg.item / q_pairs) / p.R;
                 if (q_row < p.L) mask_row = p.mask + (static_cast<size_t>(batch) * p.L + q_row) * p.L;
-                mask_vec = ((p.L & 7u) | (reinterpret_cast<uintptr_t>(p.mask) & 15u)) == 0u;
+                mask_vec = mask_row_alignment(p);
             }
             for (uint32_t jj = 0; jj < sg.len; ++jj, ++g) {
                 const uint32_t j = sg.j0 + jj;

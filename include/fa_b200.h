@@ -56,7 +56,9 @@ enum {
                                           stream's ordering guarantees are unchanged             */
     FA_B200_FLAG_FORCE_PAIR = 32u,     /* head_dim 128, no mask: always use the kernel that runs on pairs
                                           of CTAs (one MMA of 256 rows for two SMs); implies whole work
-                                          items                                                     */
+                                          items.  By default it is taken for such calls when their last
+                                          round is not divided and the sequence has an even or large
+                                          number of 256-row blocks                                   */
     FA_B200_FLAG_NO_PAIR = 64u,        /* never use that kernel                                      */
     FA_B200_FLAG_NO_SPLIT = 16u        /* never divide the key axis of one (batch, head, query rows)
                                           problem among several CTAs.  By default the warp-specialised
@@ -177,7 +179,8 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]);
 
 /*
  * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
- * kernel, 2 for the warp-specialised kernel, negative status on invalid arguments.
+ * kernel, 2 for the warp-specialised kernel, 3 for the warp-specialised kernel on pairs of CTAs
+ * (head_dim 128, no mask, whole work items), negative status on invalid arguments.
  * No counterpart in the reference.
  */
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
@@ -185,7 +188,8 @@ int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
 
 /*
  * How the warp-specialised kernel would spread a call's work over its CTAs on a device with
- * `sm_count` SMs: out[0] = kernel (1 or 2, as fa_b200_select_kernel), out[1] = CTAs launched,
+ * `sm_count` SMs: out[0] = kernel (1, 2 or 3, as fa_b200_select_kernel; for 3 a work item is 512 query
+ * rows and out[1] CTAs form out[1]/2 pairs, nothing is divided), out[1] = CTAs launched,
  * out[2] = rounds of whole work items (a work item is 256 query rows of one (batch, head) against
  * all keys; CTA c takes items c, c + out[1], ...), out[3] = work items of the last, partial round
  * whose key steps are divided evenly among the first out[6] CTAs (0 = nothing is divided; a range

@@ -95,15 +95,18 @@ def test_host_entry_rejections(lib):
 
 def test_kernel_selection(lib):
     sel = lib.fa_b200_select_kernel
-    assert sel(4, 2048, 4096, 128, 0, 0) == 2      # headline: pipelined
-    assert sel(1, 16384, 4096, 128, 0, 0) == 2
+    assert sel(4, 2048, 4096, 128, 0, 0) == 3      # headline: pipelined, on pairs of CTAs
+    assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_NO_PAIR) == 2
+    assert sel(1, 16384, 4096, 128, 0, 0) == 3
+    assert sel(1, 16384, 512, 128, 0, 0) == 2      # the last round of this one is divided: single CTAs
+    assert sel(4, 2048 + 256, 4096, 128, 0, 0) == 2    # nine 256-row blocks: an odd one would idle half a pair
     assert sel(1, 256, 256, 64, 0, 0) == 1         # tiny: simple
     assert sel(64, 197, 1024, 64, 0, 0) == 2       # 1024 items of two key steps: persistent kernel
     assert sel(64, 100, 1024, 64, 0, 0) == 1       # a single partial tile per (batch, head)
-    assert sel(1, 2048, 512, 128, 0, 0) == 2       # 32 items only, but 16 key steps each: pipelined
+    assert sel(1, 2048, 512, 128, 0, 0) == 2       # 32 items only, but 16 key steps each: pipelined (divided)
     assert sel(1, 512, 512, 128, 0, 0) == 1        # 8 items of 4 key steps cannot occupy the SMs
     assert sel(4, 2048, 512, 16, 0, 0) == 1        # small head_dim
-    assert sel(4, 2048, 4096, 128, 1, 0) == 2      # a mask does not change the choice
+    assert sel(4, 2048, 4096, 128, 1, 0) == 2      # with a mask: pipelined on single CTAs
     assert sel(4, 2048, 512, 32, 1, 0) == 1
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_FORCE_SIMPLE) == 1
     assert sel(1, 256, 256, 64, 0, _lib.FLAG_FORCE_PIPELINED) == 2

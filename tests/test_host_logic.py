@@ -99,7 +99,8 @@ def test_inputs_are_seeded_and_sliced_consistently():
 def test_every_key_step_of_every_work_item_is_scheduled_exactly_once(B, R, L, H, sms):
     """The kernel's schedule (whole items round-robin, a divided last round) restated in Python from
     what the launcher reports: full coverage, no overlap, and the limits the kernel relies on."""
-    sched = fa.describe_schedule(B, L, R * H, H, flags=fa._lib.FLAG_FORCE_PIPELINED, sm_count=sms)
+    single = fa._lib.FLAG_FORCE_PIPELINED | fa._lib.FLAG_NO_PAIR      # the kernel on single CTAs
+    sched = fa.describe_schedule(B, L, R * H, H, flags=single, sm_count=sms)
     n = sched["key_steps"]
     assert n == -(-L // 128)
     n_items = -(-L // 256) * R * B
@@ -128,12 +129,15 @@ def test_every_key_step_of_every_work_item_is_scheduled_exactly_once(B, R, L, H,
             ctas = sorted({seen[(item, j)] for j in range(n)})
             assert len(ctas) <= 3 and ctas == list(range(ctas[0], ctas[-1] + 1))   # consecutive CTAs, at most 3 parts
     # undivided on request
-    whole = fa.describe_schedule(B, L, R * H, H, flags=fa._lib.FLAG_FORCE_PIPELINED | fa._lib.FLAG_NO_SPLIT, sm_count=sms)
+    whole = fa.describe_schedule(B, L, R * H, H, flags=single | fa._lib.FLAG_NO_SPLIT, sm_count=sms)
     assert whole["tail_steps"] == 0 and whole["grid"] == min(sms, n_items)
 
 
 def test_headline_shards_are_divided_as_designed():
-    d = lambda R: fa.describe_schedule(4, 2048, R * 128, 128)
+    d = lambda R: fa.describe_schedule(4, 2048, R * 128, 128, flags=fa._lib.FLAG_NO_PAIR)
+    assert fa.describe_schedule(4, 2048, 32 * 128, 128) == {
+        "kernel": "pipelined on pairs of CTAs", "grid": 148, "full_rounds": 7, "tail_items": 0, "tail_steps": 0,
+        "key_steps": 16, "tail_grid": 0}                   # 512 work items of 512 rows on 74 pairs of SMs
     assert d(32)["tail_steps"] == 0                       # 6.92 rounds: the last one is nearly full
     # the shards of the headline job are not divided: what it would save (8, 4, 2 key steps at 2, 4, 8 GPUs) is
     # about what it costs

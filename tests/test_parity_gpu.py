@@ -420,7 +420,7 @@ def test_additive_mask(H, L):
     mask[1, :, L - L // 3:] = float("-inf")                                        # padding
     mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(1)).half()
     expected = oracle(q, k, v, H, mask)
-    for flags in kernels_for(H):
+    for flags in [f for f in kernels_for(H) if f != PAIR]:     # the kernel on pairs of CTAs takes no mask
         assert_close(run(q, k, v, H, mask=mask, flags=flags), expected)
 
 
@@ -709,7 +709,7 @@ def test_mask_against_the_reference_kernel_single_chunk(H, C):
     y_ref = _run_ref_wmma(lib, q, k, v, H, C, dmask)
     err_ref = error_metrics(y_ref.float().cpu(), expected)
     assert err_ref["max_abs"] <= 1e-2, err_ref       # the reference kernel and the oracle formula mean the same mask
-    for flags in kernels_for(H):
+    for flags in [f for f in kernels_for(H) if f != PAIR]:
         y = fa.attention_forward(H, C, q, k, v, dmask, flags=flags | _lib.FLAG_SYNC)
         torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
         assert_close(y.float().cpu(), expected)
