@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "fa_b200_select_kernel",
     "fa_b200_describe_schedule",
     "fa_b200_selftest_bounded_wait",
+    "fa_b200_selftest_debug_checks",
 )
 
 # Status codes and flags, mirrored from include/fa_b200.h.

@@ -5,7 +5,8 @@
 
   bin/fa_b200_driver  torch-free C++ program over the C ABI (fill, run, check, time)
 
-Run ``python -m fused_attention_b200.build [--ext] [--driver]``.  Nothing is installed outside the tree.
+Run ``python -m fused_attention_b200.build [--ext] [--driver] [--debug]`` (``--debug`` also builds the checked
+library ``lib/libfa_b200_debug.so``).  Nothing is installed outside the tree.
 """
 from __future__ import annotations
 
@@ -21,6 +22,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 EXTDIR = os.path.join(HERE, "ext")
 LIB = os.path.join(LIBDIR, "libfa_b200.so")
+DEBUG_LIB = os.path.join(LIBDIR, "libfa_b200_debug.so")   # the checked build (-DFA_DEBUG), used by one GPU test
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -43,21 +45,27 @@ def _stale(target: str, sources: list[str]) -> bool:
 
 
 def lib_sources() -> list[str]:
-    return [os.path.join(CSRC, f) for f in ("fa_b200.cu", "fa_kernels.cuh", "fa_ptx.cuh")] + [
+    return [os.path.join(CSRC, f) for f in ("fa_b200.cu", "fa_kernels.cuh", "fa_pair.cuh", "fa_ptx.cuh")] + [
         os.path.join(ROOT, "include", "fa_b200.h")]
 
 
-def build_lib(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/fa_b200.cu into lib/libfa_b200.so (cross-compiles without a GPU)."""
+def build_lib(force: bool = False, verbose: bool = False, debug: bool = False) -> str:
+    """Compile csrc/fa_b200.cu into lib/libfa_b200.so (cross-compiles without a GPU).
+
+    ``debug`` builds lib/libfa_b200_debug.so instead, with -DFA_DEBUG: every TMA copy and tensor-memory
+    access checks its operands first (see the checked-build section of csrc/fa_ptx.cuh)."""
     os.makedirs(LIBDIR, exist_ok=True)
-    if not force and not _stale(LIB, lib_sources()):
-        return LIB
+    out = DEBUG_LIB if debug else LIB
+    if not force and not _stale(out, lib_sources()):
+        return out
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+    if debug:
+        cmd += ["-DFA_DEBUG"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB, os.path.join(CSRC, "fa_b200.cu")]
+    cmd += ["-o", out, os.path.join(CSRC, "fa_b200.cu")]
     subprocess.run(cmd, check=True)
-    return LIB
+    return out
 
 
 def ext_path() -> str:
@@ -113,6 +121,8 @@ def build_driver(force: bool = False) -> str:
 def main(argv: list[str]) -> int:
     force = "--force" in argv
     print(build_lib(force=force, verbose="-v" in argv))
+    if "--debug" in argv:
+        print(build_lib(force=force, verbose="-v" in argv, debug=True))
     if "--ext" in argv:
         print(build_ext(force=force))
     if "--driver" in argv:

@@ -433,6 +433,12 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.cycles = g_cycles_buf;
 #endif
                 p.full_rounds = p.tail_items = p.tail_steps = p.tail_grid = 0;
+                p.part_slots = static_cast<uint32_t>(2 * c->sm_count);
+#ifdef FA_DEBUG
+                // checked build: rows the kernel fails to write stay NaN
+                if ((e = cudaMemsetAsync(y, 0xFF, static_cast<size_t>(B) * L * F * sizeof(__half), st)) != cudaSuccess)
+                    rc = static_cast<int>(e);
+#endif
                 p.part_o = nullptr;
                 p.part_ml = nullptr;
                 p.part_cnt = nullptr;
@@ -636,6 +642,7 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
         p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
         p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
         p.full_rounds = p.tail_items = p.tail_steps = p.tail_grid = 0;
+        p.part_slots = 0;
         p.part_o = nullptr;
         p.part_ml = nullptr;
         p.part_cnt = nullptr;
@@ -891,6 +898,33 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]) {
     if (e != cudaSuccess) rc = static_cast<int>(e);
     if (prev != device) (void)cudaSetDevice(prev);
     return rc;
+}
+
+int fa_b200_selftest_debug_checks(int device, uint32_t out[4]) {
+    if (!out) return FA_B200_ERR_NULL_POINTER;
+    out[0] = out[1] = out[2] = out[3] = 0;
+#ifdef FA_DEBUG
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    uint32_t* scratch = nullptr;   // {status code, reporting CTAs, launch word, bit mask of the predicates' answers}
+    e = cudaMalloc(reinterpret_cast<void**>(&scratch), 4 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(scratch, 0, 4 * sizeof(uint32_t));
+    if (e == cudaSuccess) {
+        fa::fa_selftest_debug_checks<<<1, 32>>>(scratch);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(out, scratch, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (scratch) (void)cudaFree(scratch);
+    out[2] = 1;   // this is a checked build
+    if (prev != device) (void)cudaSetDevice(prev);
+    return e != cudaSuccess ? static_cast<int>(e) : FA_B200_OK;
+#else
+    (void)device;
+    return FA_B200_OK;
+#endif
 }
 
 #ifdef FA_CYCLES

@@ -53,6 +53,7 @@ struct Params {
     float4* part_o;        // [2 * grid slots][2 tiles][H/4][128 rows] numerators of partial segments, fp32
     float2* part_ml;       // [2 * grid slots][2 tiles][128 rows] {reference maximum, row sum}
     uint32_t* part_cnt;    // [tail item][2 tiles][4 warps] parts counted in; zero between launches
+    uint32_t part_slots;   // scratch slots behind part_o / part_ml (two per CTA of the largest grid)
 #ifdef FA_CYCLES
     unsigned long long* cycles;  // 64 records (launch_id % 64) of CTA 0: {globaltimer at entry, globaltimer after the
                                  // wait for the previous kernel, globaltimer at the end, clock64 from that wait to the end}
@@ -79,6 +80,31 @@ struct TileGeom {
     static constexpr int kBoxBytes = kTile * kBoxCols * 2;     // 16 KiB at H >= 64
     static constexpr int kTileBytes = kTile * H * 2;
 };
+
+#ifdef FA_DEBUG
+// Checked build: fill in the CTA's check context (one thread) and poison its tile area with NaN (all threads).
+// The caller synchronises the CTA afterwards, before the first copy is started.
+__device__ __forceinline__ void dbg_begin(const Params& p, const WaitCtl& ctl, uint32_t smem_base, uint32_t bytes) {
+    if (threadIdx.x == 0) {
+        g_dbg.smem_lo = smem_base;
+        g_dbg.smem_hi = smem_base + bytes;
+        g_dbg.F = p.F;
+        g_dbg.L = p.L;
+        g_dbg.B = p.B;
+        g_dbg.tmem_base = 0;
+        g_dbg.tmem_cols = 512;
+        g_dbg.ctl = ctl;
+    }
+    for (uint32_t off = threadIdx.x * 16u; off < bytes; off += blockDim.x * 16u)
+        st_shared_v4(smem_base + off, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+    fence_proxy_async_smem();
+}
+// ... and, once tensor memory has been allocated, its extent (one thread; the caller synchronises).
+__device__ __forceinline__ void dbg_tmem(uint32_t base, uint32_t cols) {
+    g_dbg.tmem_base = base;
+    g_dbg.tmem_cols = cols;
+}
+#endif
 
 // Ask for one tile (all its boxes) to be brought into L2.
 template <int H>
@@ -394,6 +420,9 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
     }
+#ifdef FA_DEBUG
+    dbg_begin(p, ctl, smem_base, 3u * G::kTileBytes);
+#endif
     if (warp == 0) {
         tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
         tmem_relinquish();
@@ -401,6 +430,10 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+#ifdef FA_DEBUG
+    if (tid == 0) dbg_tmem(tmem_slot, kTmemCols);
+    __syncthreads();
+#endif
     // Everything above touched only this CTA's own state.  From here on global memory is read and
     // written: the kernel before this one in the stream must have completed.
     grid_dep_wait();
@@ -978,6 +1011,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
     }
+#ifdef FA_DEBUG
+    dbg_begin(p, ctl, smem_base, C::kSmemBytes - 1024);
+#endif
     if (warp == 12) {
         tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
         tmem_relinquish();
@@ -985,6 +1021,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+#ifdef FA_DEBUG
+    if (tid == 0) dbg_tmem(tmem_slot, C::kTmemCols);
+    __syncthreads();
+#endif
     // Barriers, TMEM and descriptors are set up; nothing of global memory has been read or written yet.
     // In a launch that was allowed to overlap the previous kernel of the stream, wait here for that
     // kernel to complete, then let the next launch's CTAs take the SMs this grid's CTAs leave (they
@@ -1499,6 +1539,11 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             bool q_pending[2] = {false, false};
             for (; k < nseg && !stop; ++k) {
                 const Seg sg = get_seg(pl_s, t0, p, k);
+#ifdef FA_DEBUG
+                if (!dbg_ok(sg.item < p.n_items && sg.len >= 1u && sg.j0 + sg.len <= p.n_kv_tiles &&
+                            (k < t0 || (seg_slot(t0, k) < p.part_slots && seg_tail_item(pl_s, t0, k) < p.tail_items)),
+                            kDbgPlan)) break;
+#endif
                 const uint32_t q_pair = sg.item % q_pairs, bh = sg.item / q_pairs;
                 const int32_t col0 = static_cast<int32_t>((bh % p.R) * H);
                 const int32_t batch = static_cast<int32_t>(bh / p.R);
@@ -1569,5 +1614,38 @@ __global__ void fa_selftest_bounded_wait(uint32_t* status, uint32_t code, long l
     __syncthreads();
     if (threadIdx.x == 0) *returned = ok ? 1u : 2u;  // 2 = gave up, as it must
 }
+
+#ifdef FA_DEBUG
+// Self-test of the checked build's predicates: no copy and no tensor-memory access is made here; the
+// predicates are asked about operands that are in order and about operands that are not, and must accept
+// the former, refuse the latter and report the first refusal.  status[3] receives one bit per answer.
+__global__ void fa_selftest_debug_checks(uint32_t* status) {
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        g_dbg.smem_lo = 0x4000;
+        g_dbg.smem_hi = 0x4000 + 64 * 1024;
+        g_dbg.F = 512;
+        g_dbg.L = 300;
+        g_dbg.B = 2;
+        g_dbg.tmem_base = 0;
+        g_dbg.tmem_cols = 256;
+        g_dbg.ctl = WaitCtl{status, &abort_flag, 1000, nullptr, 0};
+        uint32_t bits = 0;
+        bits |= dbg_copy_ok(0x4000, 4096, 64, 128, 1, false) ? 1u : 0u;          // in order
+        bits |= dbg_copy_ok(0x4000 + 1024, 4096, 64, 299, 0, true) ? 2u : 0u;    // in order (a store at the last row)
+        bits |= dbg_tmem_ok(128u, 32u) ? 4u : 0u;                                // in order (warp 0, lanes 0-31)
+        bits |= dbg_copy_ok(0x4000, 4096, 68, 0, 0, false) ? 0u : 8u;            // x not a multiple of 8: refused first
+        bits |= dbg_copy_ok(0x4000 + 62 * 1024, 4096, 0, 0, 0, false) ? 0u : 16u;   // runs past the tile area
+        bits |= dbg_copy_ok(0x4000 + 512, 4096, 0, 0, 0, false) ? 0u : 32u;      // not on a 1024-byte boundary
+        bits |= dbg_copy_ok(0x4000, 4096, 0, 300, 0, true) ? 0u : 64u;           // a store beyond the last row
+        bits |= dbg_copy_ok(0x4000, 4096, 0, -1, 0, true) ? 0u : 128u;           // a store at a negative row
+        bits |= dbg_copy_ok(0x4000, 4096, 0, 0, 2, false) ? 0u : 256u;           // batch entry outside the tensor
+        bits |= dbg_tmem_ok(240u, 32u) ? 0u : 512u;                              // columns beyond the allocation
+        bits |= dbg_tmem_ok((32u << 16) | 0u, 16u) ? 0u : 1024u;                 // another warp's lanes
+        status[3] = bits;
+    }
+}
+#endif
 
 }  // namespace fa

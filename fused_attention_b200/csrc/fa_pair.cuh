@@ -135,12 +135,18 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         prefetch_tensormap(&tmKh);
         prefetch_tensormap(&tmV);
     }
+#ifdef FA_DEBUG
+    dbg_begin(p, ctl, smem_base, C::kSmemBytes - 1024);
+#endif
     if (warp == 12) {
         tmem_alloc_pair(smem_u32(&tmem_slot), C::kTmemCols);
         tmem_relinquish_pair();
     }
     tc_fence_before();
     __syncthreads();
+#ifdef FA_DEBUG
+    if (tid == 0) dbg_tmem(tmem_slot, C::kTmemCols);
+#endif
     // both CTAs have their barriers and their tensor memory before either signals or multiplies anything
     cluster_arrive();
     cluster_wait();

@@ -174,6 +174,62 @@ __device__ __forceinline__ bool mbar_wait_certain(uint32_t bar, uint32_t parity,
     return true;
 }
 
+// ----------------------------------------------------------------------------- checked build (-DFA_DEBUG)
+// With -DFA_DEBUG every TMA copy and every tensor-memory access of the kernels checks its operands first:
+// the shared-memory side lies inside the CTA's tile area and on a 1024-byte boundary, the innermost
+// coordinate is a multiple of 8 elements (16 bytes) and all coordinates lie inside the tensor, a store does
+// not start at a negative or out-of-range row, a tensor-memory access stays inside the CTA's allocation and
+// on the lanes of the issuing warp.  A failed check records kRoleDebug | <what> in the device status word,
+// sets the CTA's abort flag and SKIPS the access (nothing faults; the bounded waits then return at once and
+// the CTA leaves).  The kernels also fill their tile area with NaN before the first copy, and the launcher
+// fills Y with NaN before the launch, so that anything consumed before it has landed, or never written,
+// shows in the result.  Normal builds contain none of this.
+#ifdef FA_DEBUG
+constexpr uint32_t kRoleDebug = 0x700u;
+enum : uint32_t {
+    kDbgSmemRange = 1,   // shared-memory operand of a copy outside the tile area
+    kDbgSmemAlign,       // ... not on a 1024-byte boundary
+    kDbgTmaX,            // innermost coordinate not a multiple of 8 elements
+    kDbgTmaCoord,        // a coordinate outside the tensor
+    kDbgStoreRow,        // a store starting at a negative row or beyond the last row
+    kDbgTmemCols,        // tensor-memory columns outside the allocation
+    kDbgTmemLanes,       // tensor-memory lanes that are not the issuing warp's
+    kDbgPlan             // a work item, key step or scratch slot outside its range
+};
+struct DbgCtx {
+    uint32_t smem_lo, smem_hi;   // the CTA's tile area in shared memory (shared-window addresses)
+    uint32_t F, L, B;            // extent of the tensors in elements / rows / batch entries
+    uint32_t tmem_base, tmem_cols;
+    WaitCtl ctl;
+};
+__shared__ DbgCtx g_dbg;   // one per CTA, filled by one thread of each kernel before anything is checked
+
+__device__ __forceinline__ bool dbg_ok(bool cond, uint32_t what) {
+    if (!cond) wait_expired(g_dbg.ctl, kRoleDebug | what);
+    return cond;
+}
+__device__ __forceinline__ bool dbg_copy_ok(uint32_t saddr, uint32_t bytes, int32_t x, int32_t y, int32_t z, bool store) {
+    bool ok = dbg_ok(saddr >= g_dbg.smem_lo && saddr + bytes <= g_dbg.smem_hi, kDbgSmemRange);
+    ok &= dbg_ok((saddr & 1023u) == 0u, kDbgSmemAlign);
+    ok &= dbg_ok((x & 7) == 0, kDbgTmaX);
+    ok &= dbg_ok(x >= 0 && static_cast<uint32_t>(x) < g_dbg.F && z >= 0 && static_cast<uint32_t>(z) < g_dbg.B, kDbgTmaCoord);
+    if (store) ok &= dbg_ok(y >= 0 && static_cast<uint32_t>(y) < g_dbg.L, kDbgStoreRow);
+    else ok &= dbg_ok(y >= 0, kDbgTmaCoord);   // a load may run past the last row (zero fill), never start before the first
+    return ok;
+}
+__device__ __forceinline__ bool dbg_tmem_ok(uint32_t taddr, uint32_t ncols) {
+    const uint32_t col = taddr & 0xFFFFu, base = g_dbg.tmem_base & 0xFFFFu;
+    bool ok = dbg_ok(col >= base && col + ncols <= base + g_dbg.tmem_cols, kDbgTmemCols);
+    ok &= dbg_ok(((taddr >> 16) & 0x7Fu) == ((threadIdx.x >> 5) & 3u) * 32u, kDbgTmemLanes);
+    return ok;
+}
+#define FA_DBG_COPY(saddr, bytes, x, y, z, store) if (!dbg_copy_ok(saddr, bytes, x, y, z, store)) return
+#define FA_DBG_TMEM(taddr, ncols) if (!dbg_tmem_ok(taddr, ncols)) return
+#else
+#define FA_DBG_COPY(saddr, bytes, x, y, z, store) do {} while (0)
+#define FA_DBG_TMEM(taddr, ncols) do {} while (0)
+#endif
+
 // ----------------------------------------------------------------------------- launch overlap
 // Programmatic dependent launch.  A kernel launched with the "programmatic stream serialization"
 // attribute may become resident while the kernel before it in the stream is still running;
@@ -192,6 +248,7 @@ __device__ __forceinline__ void prefetch_tensormap(const void* map) {
 // x is the innermost coordinate; x * sizeof(element) must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int32_t x,
                                             int32_t y, int32_t z) {
+    FA_DBG_COPY(dst, 4096u, x, y, z, false);
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
@@ -210,6 +267,7 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const void* map, int32_t x, i
 // 3-D tiled store shared -> global as one bulk group; the box is clipped at the tensor's bounds.
 // Coordinates must not be negative; x * sizeof(element) must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int32_t x, int32_t y, int32_t z) {
+    FA_DBG_COPY(src, 4096u, x, y, z, true);
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(map)),
                  "r"(src), "r"(x), "r"(y), "r"(z)
@@ -310,6 +368,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 // 32 lanes x 32 columns of 32-bit cells: thread t of the warp receives lane (base lane + t),
 // register i holds column (base column + i).  A warp may only touch lanes [32*(warp%4), +32).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    FA_DBG_TMEM(taddr, 32u);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -323,6 +382,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    FA_DBG_TMEM(taddr, 16u);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -333,6 +393,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    FA_DBG_TMEM(taddr, 32u);
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -346,6 +407,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+    FA_DBG_TMEM(taddr, 16u);
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
@@ -426,6 +488,7 @@ __host__ __device__ constexpr uint32_t make_idesc_f16_pair(uint32_t n, uint32_t 
 // to the other CTA of the pair (`bar` is a shared::cluster address).
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, uint32_t bar, int32_t x, int32_t y,
                                                  int32_t z) {
+    FA_DBG_COPY(dst, 4096u, x, y, z, false);
     asm volatile(
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),

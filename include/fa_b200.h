@@ -178,6 +178,19 @@ int fa_b200_read_status(int device, uint32_t out[2]);
 int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]);
 
 /*
+ * The checked build of the library (compiled with -DFA_DEBUG: every TMA copy and tensor-memory access
+ * checks its shared-memory operand, its coordinates and its columns first, records a failed check in
+ * the device status word and skips the access; tile buffers and Y are filled with NaN beforehand) can
+ * test its own predicates: they are asked about operands that are in order and operands that are not,
+ * with no copy made.  out[0] = status code recorded by the first refusal (expected 0x703: innermost
+ * coordinate not a multiple of 8 elements), out[1] = 1, out[2] = 1 in a checked build and 0 in a normal
+ * one (where nothing else is done), out[3] = one bit per predicate answered as it should be (expected
+ * 0x7FF).  It plays the role of the reference's -g -G build of its smoke test (CMakeLists.txt:43) on
+ * a pool where compute-sanitizer cannot be run.
+ */
+int fa_b200_selftest_debug_checks(int device, uint32_t out[4]);
+
+/*
  * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
  * kernel, 2 for the warp-specialised kernel, 3 for the warp-specialised kernel on pairs of CTAs
  * (head_dim 128, no mask, whole work items), negative status on invalid arguments.

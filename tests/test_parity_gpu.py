@@ -614,6 +614,57 @@ def test_more_batch_entries_than_a_grid_axis_holds():
     assert float(d.max()) <= MAX_ABS_TOL and float(d.mean()) <= MEAN_ABS_TOL
 
 
+# ---------------------------------------------------------------- the checked build
+def _checked_lib():
+    path = os.path.join(os.path.dirname(fa.__file__), "lib", "libfa_b200_debug.so")
+    if not os.path.exists(path):
+        pytest.skip("checked library not built (python -m fused_attention_b200.build --debug)")
+    lib = ctypes.CDLL(path)
+    u32, vp, i32 = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
+    lib.fa_b200_attention_forward.restype = i32
+    lib.fa_b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
+    lib.fa_b200_read_status.restype = i32
+    lib.fa_b200_read_status.argtypes = [i32, ctypes.POINTER(u32)]
+    lib.fa_b200_selftest_debug_checks.restype = i32
+    lib.fa_b200_selftest_debug_checks.argtypes = [i32, ctypes.POINTER(u32)]
+    return lib
+
+
+def test_checked_build_refuses_bad_operands_without_touching_memory():
+    """The predicates of the checked build (-DFA_DEBUG), asked about operands that are in order and operands
+    that are not; no copy is made.  The normal library has no checks and says so."""
+    out = (ctypes.c_uint32 * 4)()
+    assert _checked_lib().fa_b200_selftest_debug_checks(0, out) == 0
+    assert (out[0], out[1], out[2], out[3]) == (0x703, 1, 1, 0x7FF)
+    assert _lib.load().fa_b200_selftest_debug_checks(0, out) == 0 and out[2] == 0
+
+
+@pytest.mark.parametrize("H,B,R,L,flags,masked", [
+    (16, 2, 3, 200, SIMPLE, False), (64, 2, 3, 300, SIMPLE, True), (64, 3, 5, 700, ONE, False), (64, 2, 2, 520, ONE, True),
+    (128, 2, 3, 1000, ONE, False), (128, 2, 4, 2048, PAIR, False), (128, 1, 4, 2048 + 77, 0, False), (128, 1, 2, 650, ONE, True),
+    (128, 20, 10, 300, PAIR, False)])
+def test_checked_build_runs_clean_and_gives_the_same_bits(H, B, R, L, flags, masked):
+    """Every kernel under the checked build: each TMA copy and tensor-memory access is checked against the
+    CTA's tile area, the tensor's extent and the CTA's tensor-memory allocation, tile buffers and Y are
+    filled with NaN beforehand.  No check may fire, no NaN may survive, and the bits are the normal build's."""
+    lib = _checked_lib()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(L + H)
+    q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() for _ in range(3))
+    mask = None
+    if masked:
+        mask = torch.triu(torch.full((L, L), float("-inf"), device="cuda", dtype=torch.float16), diagonal=1)
+        mask = mask.unsqueeze(0).expand(B, L, L).contiguous()
+    y = torch.empty_like(q)
+    rc = lib.fa_b200_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), None if mask is None else mask.data_ptr(),
+                                       y.data_ptr(), B, L, R * H, H, 0, 0, None, flags | _lib.FLAG_SYNC)
+    assert rc == 0, rc
+    w = (ctypes.c_uint32 * 2)()
+    assert lib.fa_b200_read_status(0, w) == 0 and (w[0], w[1]) == (0, 0), hex(w[0])
+    assert torch.isfinite(y).all()
+    assert torch.equal(y, fa.attention_forward(H, 16 if H < 128 else 32, q, k, v, mask, flags=flags | _lib.FLAG_SYNC))
+
+
 # ---------------------------------------------------------------- drop-in module `fused_attn`
 def _fused_attn_module():
     ext_dir = os.path.join(os.path.dirname(fa.__file__), "ext")
