@@ -164,6 +164,19 @@ int make_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L, uint32_
     return r == CUDA_SUCCESS ? FA_B200_OK : FA_B200_ERR_DRIVER;
 }
 
+// 3-D map {L keys, L rows, B} over a contiguous [B, L, L] fp16 mask; box = 128 rows x 64 keys.  Needs rows that
+// start on 16-byte boundaries (L a multiple of 8, base aligned); the caller checks.
+int make_mask_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L) {
+    const cuuint64_t dims[3] = {L, L, B};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(L) * 2ull, static_cast<cuuint64_t>(L) * 2ull * L};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(fa::kTile), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FA_B200_OK : FA_B200_ERR_DRIVER;
+}
+
 bool is_pow2(uint32_t x) { return x != 0 && (x & (x - 1)) == 0; }
 
 int validate(const void* q, const void* k, const void* v, const void* mask, const void* y, uint32_t B,
@@ -296,9 +309,9 @@ int launch_simple(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorM
 
 template <int H, bool M>
 int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtensorMap& mk,
-                     const CUtensorMap& mv, const CUtensorMap& my, const Params& p, uint32_t n_ctas,
-                     cudaStream_t st, bool overlap) {
-    constexpr int smem = fa::PipeCfg<H>::kSmemBytes;
+                     const CUtensorMap& mv, const CUtensorMap& my, const CUtensorMap& mm, const Params& p,
+                     uint32_t n_ctas, cudaStream_t st, bool overlap) {
+    constexpr int smem = fa::PipeCfg<H, M>::kSmemBytes;
     auto kern = fa::fa_fwd_pipelined<H, M>;
     if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {   // setting it twice is harmless
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -306,7 +319,7 @@ int launch_pipelined(DeviceCtx& c, int slot, const CUtensorMap& mq, const CUtens
         c.attr_done.fetch_or(1u << slot, std::memory_order_release);
     }
     const dim3 grid(n_ctas, 1, 1);   // persistent: at most one CTA per SM
-    const cudaError_t e = launch_kernel(kern, grid, 512, smem, st, overlap, mq, mk, mv, my, p);
+    const cudaError_t e = launch_kernel(kern, grid, 512, smem, st, overlap, mq, mk, mv, my, mm, p);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
@@ -429,6 +442,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                 p.n_items = p.q_pairs * p.R * B;
                 p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
                 p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+                p.mask_tma = 0;
 #ifdef FA_CYCLES
                 p.cycles = g_cycles_buf;
 #endif
@@ -477,12 +491,19 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                         }
                     }
                     if (rc == FA_B200_OK && !done) {
-                        if (mask)
-                            rc = H == 128 ? launch_pipelined<128, true>(*c, 10, mq, mk, mv, my, p, sch.grid, st, overlap)
-                                          : launch_pipelined<64, true>(*c, 11, mq, mk, mv, my, p, sch.grid, st, overlap);
-                        else
-                            rc = H == 128 ? launch_pipelined<128, false>(*c, 8, mq, mk, mv, my, p, sch.grid, st, overlap)
-                                          : launch_pipelined<64, false>(*c, 9, mq, mk, mv, my, p, sch.grid, st, overlap);
+                        if (mask) {
+                            // mask tiles through TMA when every mask row starts on a 16-byte boundary; else the
+                            // softmax threads read their rows straight from global memory
+                            CUtensorMap mm = mq;
+                            p.mask_tma = ((L & 7u) == 0u && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0u) ? 1u : 0u;
+                            if (p.mask_tma) rc = make_mask_map(&mm, mask, B, L);
+                            if (rc == FA_B200_OK)
+                                rc = H == 128 ? launch_pipelined<128, true>(*c, 10, mq, mk, mv, my, mm, p, sch.grid, st, overlap)
+                                              : launch_pipelined<64, true>(*c, 11, mq, mk, mv, my, mm, p, sch.grid, st, overlap);
+                        } else {
+                            rc = H == 128 ? launch_pipelined<128, false>(*c, 8, mq, mk, mv, my, mq, p, sch.grid, st, overlap)
+                                          : launch_pipelined<64, false>(*c, 9, mq, mk, mv, my, mq, p, sch.grid, st, overlap);
+                        }
                     }
                 } else if (mask) {
                     switch (H) {
@@ -641,6 +662,7 @@ int fa_b200_attention_forward_noalloc(const void* q, const void* k, const void* 
         p.n_items = p.q_pairs * p.R * B;
         p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(H)));
         p.mask_to_score = static_cast<float>(std::sqrt(static_cast<double>(H)));
+        p.mask_tma = 0;
         p.full_rounds = p.tail_items = p.tail_steps = p.tail_grid = 0;
         p.part_slots = 0;
         p.part_o = nullptr;

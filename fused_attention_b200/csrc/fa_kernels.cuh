@@ -45,6 +45,7 @@ struct Params {
     uint32_t n_items;     // q_pairs * R * B: work items of the pipelined kernel
     float scale_log2;     // log2(e) / sqrt(H)
     float mask_to_score;  // sqrt(H): mask value m enters as s + m*sqrt(H) before the folded scale
+    uint32_t mask_tma;    // pipelined kernel with a mask: 1 = mask tiles come through TMA (rows 16-byte aligned)
     // schedule of the pipelined kernel (see Plan) and the scratch of a divided tail round
     uint32_t full_rounds;  // rounds of whole items: item = cta + k * grid
     uint32_t tail_items;   // items after the full rounds whose key steps are divided among the CTAs
@@ -372,6 +373,27 @@ __device__ __forceinline__ void add_mask_row(float (&s)[kTile], const __half* mr
     }
 }
 
+// The same from a mask tile that TMA has brought into shared memory: two boxes of 128 rows x 64 keys, rows of
+// 128 bytes with the 128-byte swizzle (16-byte chunk c of row r lies at chunk c ^ (r & 7)).  Keys and rows
+// beyond the end of the sequence were filled with zeros.
+__device__ __forceinline__ void add_mask_tile_row(float (&s)[kTile], uint32_t smask, uint32_t row, float to_score) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+            ld_shared_v4(smask + b * (kTile * 128) + row * 128u + ((static_cast<uint32_t>(c) ^ (row & 7u)) * 16u), w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                const int i = b * 64 + c * 8 + 2 * e;
+                s[i] = fmaf(f.x, to_score, s[i]);
+                s[i + 1] = fmaf(f.y, to_score, s[i + 1]);
+            }
+        }
+    }
+}
+
 // What every mask row start of a call is aligned to: rows are L fp16 values apart from the base address.
 __device__ __forceinline__ uint32_t mask_row_alignment(const Params& p) {
     const uint32_t bits = (p.L * 2u) | static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.mask));
@@ -543,14 +565,16 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 }
 
 // ============================================================================ pipelined kernel
-template <int H>
+template <int H, bool kHasMask = false>
 struct PipeCfg {
     using G = TileGeom<H>;
-    static constexpr int kStages = H == 128 ? 4 : 8;   // ring slots of one K or V tile each
+    // ring slots of one K or V tile each; with a mask a quarter of the ring makes room for one mask tile
+    static constexpr int kStages = (H == 128 ? 4 : 8) * (kHasMask ? 3 : 4) / 4;
     static constexpr int kQBytes = 2 * G::kTileBytes;  // two query tiles
     static constexpr int kRingBytes = kStages * G::kTileBytes;
+    static constexpr int kMaskBytes = kHasMask ? kTile * kTile * 2 : 0;   // one 128 x 128 fp16 mask tile (two boxes of 64 keys)
     static constexpr int kStageBytes = 4 * 32 * 128;   // epilogue staging: per warp 32 rows x 64 fp16
-    static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kQBytes + kRingBytes + kMaskBytes + kStageBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
     // TMEM columns.  P (fp16, 64 columns per tile) has columns of its own instead of overwriting its
     // S: the next Q K^T of a tile then does not have to wait for the P V that reads P, only for the
@@ -921,9 +945,9 @@ template <int H, bool kHasMask>
 __global__ void __launch_bounds__(512, 1)
 fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmY,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap tmM, const Params p) {
     using G = TileGeom<H>;
-    using C = PipeCfg<H>;
+    using C = PipeCfg<H, kHasMask>;
     constexpr int NS = C::kStages;
     enum {
         BAR_QFULL0 = 0, BAR_QFULL1,  // TMA -> MMA: query tile landed
@@ -937,6 +961,10 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_A0, BAR_A1,              // softmax -> epilogue: final row sums in shared memory (4)
         BAR_OFREE0, BAR_OFREE1,      // epilogue -> MMA, softmax: O tile read out (4 arrivals)
         BAR_EPI,                     // epilogue -> softmax: the epilogue warps are through (4 arrivals)
+        BAR_MFULL0, BAR_MFULL1,      // TMA -> softmax of tile i: its mask tile of this key step landed (one buffer,
+                                     // filled for the two tiles in turn; a barrier per tile, one phase per key step,
+                                     // so that a tile can never take the other tile's phase for its own)
+        BAR_MEMPTY0, BAR_MEMPTY1,    // softmax of tile i -> TMA: the mask tile has been read (4 arrivals)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FINAL2,                  // the same for the second issuing warp
         BAR_FULL,                    // NS ring barriers TMA -> MMA
@@ -965,7 +993,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;                   // two tiles
     const uint32_t sRing = smem_base + C::kQBytes;   // NS tiles
-    const uint32_t sStage = sRing + C::kRingBytes;   // epilogue staging, 4 KiB per epilogue warp
+    const uint32_t sMask = sRing + C::kRingBytes;    // one mask tile (instances with a mask only)
+    const uint32_t sStage = sMask + C::kMaskBytes;   // epilogue staging, 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
     const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles, p.status + 2, p.launch_id};
@@ -999,7 +1028,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // one arrival per warp (after __syncwarp), not per thread: 128 arrivals on one
             // shared-memory word serialise
             const bool per_warp = (i == BAR_P0 || i == BAR_P1 || i == BAR_SFREE0 || i == BAR_SFREE1 ||
-                                   i == BAR_A0 || i == BAR_A1 || i == BAR_EPI ||
+                                   i == BAR_A0 || i == BAR_A1 || i == BAR_EPI || i == BAR_MEMPTY0 || i == BAR_MEMPTY1 ||
                                    i == BAR_OFREE0 || i == BAR_OFREE1);
             mbar_init(bar(i), per_warp ? 4u : 1u);
         }
@@ -1010,6 +1039,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
+        if constexpr (kHasMask) prefetch_tensormap(&tmM);
     }
 #ifdef FA_DEBUG
     dbg_begin(p, ctl, smem_base, C::kSmemBytes - 1024);
@@ -1089,9 +1119,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
                 if constexpr (kHasMask) {
-                    if (mask_row != nullptr)
+                    if (p.mask_tma != 0u) {
+                        // The mask tile of this tile and step, brought in by TMA into the one mask buffer; it is
+                        // handed back as soon as it has been read.
+                        mbar_wait(bar(BAR_MFULL0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_MFULL0 + i));
+                        add_mask_tile_row(s, sMask, row, p.mask_to_score);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(BAR_MEMPTY0 + i));
+                    } else if (mask_row != nullptr) {
                         add_mask_row(s, mask_row + static_cast<size_t>(j) * kTile,
                                      min(static_cast<int>(p.L - j * kTile), kTile), p.mask_to_score, mask_vec);
+                    }
                 }
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
                 if (first) m = row_max(s);   // first key tile of the segment: the reference is its row maximum
@@ -1578,6 +1616,41 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     while (q_pending[tt] && !mbar_try_wait(bar(BAR_QFULL0 + tt), (k > 0 ? k - 1u : 0u) & 1u) &&
                            clock64() - t0 < 200000000LL) {
                     }
+                }
+            }
+        } else if (kHasMask && warp == 15 && p.mask_tma != 0u && elect_one()) {
+            // -------------------------------------------------------------- TMA producer of the mask tiles
+            // One buffer, filled for tile 0 and tile 1 of every key step in turn, each time as soon as the softmax
+            // warps of the tile before have read it: tile 1 of step g follows tile 0 of step g, tile 0 of step g
+            // follows tile 1 of step g - 1.  Boxes that lie beyond the end of the sequence (keys or rows) arrive
+            // as zeros.
+            uint32_t g = 0;   // global step
+            bool stop = false;
+            for (uint32_t k = 0; k < nseg && !stop; ++k) {
+                const Seg sg = get_seg(pl_s, t0, p, k);
+                const int32_t batch = static_cast<int32_t>((sg.item / q_pairs) / p.R);
+                const int32_t q_row0 = static_cast<int32_t>((sg.item % q_pairs) * 2u * kTile);
+                for (uint32_t jj = 0; jj < sg.len && !stop; ++jj, ++g) {
+                    const int32_t key0 = static_cast<int32_t>((sg.j0 + jj) * kTile);
+                    for (uint32_t i = 0; i < 2; ++i) {
+                        bool ok = true;
+                        if (i == 1) ok = mbar_wait(bar(BAR_MEMPTY0), g & 1u, ctl, kRoleProducer | BAR_MEMPTY0);
+                        else if (g > 0) ok = mbar_wait(bar(BAR_MEMPTY1), (g - 1u) & 1u, ctl, kRoleProducer | BAR_MEMPTY1);
+                        if (!ok) {
+                            stop = true;
+                            break;
+                        }
+                        mbar_expect_tx(bar(BAR_MFULL0 + i), C::kMaskBytes);
+                        tma_load_3d(sMask, &tmM, bar(BAR_MFULL0 + i), key0, q_row0 + static_cast<int32_t>(i * kTile), batch);
+                        tma_load_3d(sMask + kTile * 128, &tmM, bar(BAR_MFULL0 + i), key0 + 64,
+                                    q_row0 + static_cast<int32_t>(i * kTile), batch);
+                    }
+                }
+            }
+            if (abort_flag != 0u && g > 0u) {   // do not leave while the last mask tiles may still be landing
+                const long long t_0 = clock64();
+                while (!(mbar_try_wait(bar(BAR_MFULL0), (g - 1u) & 1u) && mbar_try_wait(bar(BAR_MFULL1), (g - 1u) & 1u)) &&
+                       clock64() - t_0 < 200000000LL) {
                 }
             }
         }

@@ -208,11 +208,13 @@ __device__ __forceinline__ bool dbg_ok(bool cond, uint32_t what) {
     if (!cond) wait_expired(g_dbg.ctl, kRoleDebug | what);
     return cond;
 }
+// (the innermost extent is F for Q, K, V, Y and L for the mask: a copy whose x lies below max(F, L) passes here)
 __device__ __forceinline__ bool dbg_copy_ok(uint32_t saddr, uint32_t bytes, int32_t x, int32_t y, int32_t z, bool store) {
     bool ok = dbg_ok(saddr >= g_dbg.smem_lo && saddr + bytes <= g_dbg.smem_hi, kDbgSmemRange);
     ok &= dbg_ok((saddr & 1023u) == 0u, kDbgSmemAlign);
     ok &= dbg_ok((x & 7) == 0, kDbgTmaX);
-    ok &= dbg_ok(x >= 0 && static_cast<uint32_t>(x) < g_dbg.F && z >= 0 && static_cast<uint32_t>(z) < g_dbg.B, kDbgTmaCoord);
+    const uint32_t x_extent = (g_dbg.F > g_dbg.L ? g_dbg.F : g_dbg.L) + (store ? 0u : 128u);   // a load may start in the zero fill
+    ok &= dbg_ok(x >= 0 && static_cast<uint32_t>(x) < x_extent && z >= 0 && static_cast<uint32_t>(z) < g_dbg.B, kDbgTmaCoord);
     if (store) ok &= dbg_ok(y >= 0 && static_cast<uint32_t>(y) < g_dbg.L, kDbgStoreRow);
     else ok &= dbg_ok(y >= 0, kDbgTmaCoord);   // a load may run past the last row (zero fill), never start before the first
     return ok;
@@ -285,6 +287,9 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&w)[4]) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+}
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }

@@ -446,6 +446,26 @@ def test_additive_mask_rows_at_any_alignment(L):
         assert_close(y.float().cpu(), expected)
 
 
+@pytest.mark.parametrize("B,R,L,H", [(2, 8, 2048, 128), (2, 8, 2048, 64), (4, 32, 2048, 128), (1, 3, 1000, 128), (3, 4, 1336, 64)])
+def test_additive_mask_on_long_sequences(B, R, L, H):
+    """The warp-specialised kernel brings the mask in tile by tile through TMA into one buffer that the two query
+    tiles of a CTA use in turn; many key steps and many work items per CTA, where the two tiles drift apart in
+    time.  Causal mask plus a soft random part; against fp32 attention with the mask on the same GPU."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(L + H)
+    q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() * 0.5 for _ in range(3))
+    mask = torch.triu(torch.full((L, L), float("-inf"), device="cuda", dtype=torch.float16), diagonal=1)
+    mask = mask.unsqueeze(0).repeat(B, 1, 1)
+    mask += (0.5 * torch.randn(B, L, L, generator=g, device="cuda")).half()
+    y = fa.attention_forward(H, 32, q, k, v, mask, flags=ONE | _lib.FLAG_SYNC)
+    y2 = fa.attention_forward(H, 32, q, k, v, mask, flags=ONE | _lib.FLAG_SYNC)
+    assert torch.equal(y, y2) and torch.isfinite(y).all()
+    qf, kf, vf = (t.float().view(B, L, R, H).transpose(1, 2) for t in (q, k, v))
+    ref = (torch.softmax(qf @ kf.mT / H ** 0.5 + mask.float()[:, None], -1) @ vf).transpose(1, 2).reshape(B, L, R * H)
+    d = (y.float() - ref).abs()
+    assert float(d.max()) <= MAX_ABS_TOL and float(d.mean()) <= MEAN_ABS_TOL, (float(d.max()), float(d.mean()))
+
+
 def test_value_of_ones_gives_ones_at_full_size():
     w = WORKLOADS["llama7b_prefill"]
     q, k, _ = workload_inputs(w)
