@@ -47,6 +47,7 @@ struct DeviceCtx {
     uint32_t* status = nullptr;   // device memory: {first failure code, reporting CTA count, id of the launch that reported, -}
     std::atomic<uint32_t> attr_done{0};   // bit per kernel instance whose smem attribute is set
     std::atomic<int> pair_clusters{-1};    // how many CTA pairs of fa_fwd_pair the device holds at once (-1: not asked yet)
+    std::atomic<int> pair_clusters_mask{-1};   // the same for the instance with a mask
     // Scratch of launches that divide their last round of work items (fa::Plan): one buffer per stream,
     // because launches on different streams may run at the same time.  kSplitPool buffers are allocated
     // with the context; a launch on a stream that finds none free runs undivided.
@@ -179,6 +180,11 @@ int make_mask_map(CUtensorMap* map, const void* base, uint32_t B, uint32_t L) {
 
 bool is_pow2(uint32_t x) { return x != 0 && (x & (x - 1)) == 0; }
 
+// Whether TMA can fetch tiles of the mask: every row of it starts on a 16-byte boundary.
+bool mask_rows_aligned(const void* mask, uint32_t L) {
+    return (L & 7u) == 0u && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0u;
+}
+
 int validate(const void* q, const void* k, const void* v, const void* mask, const void* y, uint32_t B,
              uint32_t L, uint32_t F, uint32_t H, uint32_t chunk, uint32_t flags) {
     if (!q || !k || !v || !y) return FA_B200_ERR_NULL_POINTER;
@@ -200,7 +206,8 @@ int validate(const void* q, const void* k, const void* v, const void* mask, cons
                            FA_B200_FLAG_NO_OVERLAP | FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR | FA_B200_FLAG_NO_PAIR;
     if (flags & ~known) return FA_B200_ERR_FLAGS;
     if (flags & FA_B200_FLAG_FORCE_PAIR) {
-        if (H != 128 || mask || (flags & (FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_NO_PAIR))) return FA_B200_ERR_FLAGS;
+        if (H != 128 || (mask && !mask_rows_aligned(mask, L)) || (flags & (FA_B200_FLAG_FORCE_SIMPLE | FA_B200_FLAG_NO_PAIR)))
+            return FA_B200_ERR_FLAGS;
     }
     if ((flags & FA_B200_FLAG_FORCE_SIMPLE) && (flags & FA_B200_FLAG_FORCE_PIPELINED)) return FA_B200_ERR_FLAGS;
     if ((flags & FA_B200_FLAG_FORCE_PIPELINED) && H < 64) return FA_B200_ERR_FLAGS;
@@ -344,25 +351,27 @@ const SplitScratch* scratch_for_stream(DeviceCtx& c, cudaStream_t st) {
     return nullptr;
 }
 
-// When the kernel on pairs of CTAs is taken: head_dim 128, no mask, whole work items (a call whose last
+// When the kernel on pairs of CTAs is taken: head_dim 128, a mask only if TMA can fetch its tiles (every row
+// on a 16-byte boundary), whole work items (a call whose last
 // round is divided stays on single CTAs), and a number of 256-row blocks per (batch, head) that is even or
 // large, since a pair works on 512 rows and an odd block leaves one CTA of a pair without work.  Measured on
 // the headline shape: the same SM clocks per launch as on single CTAs, but less shared-memory and L2 traffic,
 // so under the power cap the SMs clock 2 to 3 % higher.
-bool use_pair_kernel(uint32_t H, bool has_mask, uint32_t q_pairs, uint32_t tail_steps, uint32_t flags) {
-    if (H != 128 || has_mask || (flags & FA_B200_FLAG_NO_PAIR)) return false;
+bool use_pair_kernel(uint32_t H, bool mask_ok, uint32_t q_pairs, uint32_t tail_steps, uint32_t flags) {
+    if (H != 128 || !mask_ok || (flags & FA_B200_FLAG_NO_PAIR)) return false;
     if (flags & FA_B200_FLAG_FORCE_PAIR) return true;
     if (tail_steps != 0) return false;
     return (q_pairs % 2u) == 0u || q_pairs >= 16u;
 }
 
 // The pair kernel: clusters of two CTAs, as many as the device holds at once (asked once per device).
+template <bool kHasMask>
 int launch_pair(DeviceCtx& c, const CUtensorMap& mq, const CUtensorMap& mkh, const CUtensorMap& mv,
-                const CUtensorMap& my, const Params& p, uint32_t n_quad_items, cudaStream_t st, bool overlap,
-                bool* launched) {
-    constexpr int smem = fa::PairCfg::kSmemBytes;
-    constexpr int slot = 12;
-    auto kern = fa::fa_fwd_pair;
+                const CUtensorMap& my, const CUtensorMap& mm, const Params& p, uint32_t n_quad_items,
+                cudaStream_t st, bool overlap, bool* launched) {
+    constexpr int smem = fa::PairCfgT<kHasMask>::kSmemBytes;
+    constexpr int slot = kHasMask ? 13 : 12;
+    auto kern = fa::fa_fwd_pair<kHasMask>;
     *launched = false;
     if (!(c.attr_done.load(std::memory_order_acquire) & (1u << slot))) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -381,7 +390,8 @@ int launch_pair(DeviceCtx& c, const CUtensorMap& mq, const CUtensorMap& mkh, con
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    int clusters = c.pair_clusters.load(std::memory_order_acquire);
+    std::atomic<int>& held = kHasMask ? c.pair_clusters_mask : c.pair_clusters;
+    int clusters = held.load(std::memory_order_acquire);
     if (clusters < 0) {
         cfg.gridDim = dim3(static_cast<unsigned>(c.sm_count) & ~1u, 1, 1);
         cfg.numAttrs = 1;
@@ -391,14 +401,14 @@ int launch_pair(DeviceCtx& c, const CUtensorMap& mq, const CUtensorMap& mkh, con
             n = 0;
         }
         if (n > c.sm_count / 2) n = c.sm_count / 2;
-        c.pair_clusters.store(n, std::memory_order_release);
+        held.store(n, std::memory_order_release);
         clusters = n;
     }
     if (clusters <= 0) return FA_B200_OK;   // the device cannot hold a pair: the caller takes the other kernel
     const uint32_t nc = n_quad_items < static_cast<uint32_t>(clusters) ? n_quad_items : static_cast<uint32_t>(clusters);
     cfg.gridDim = dim3(2 * nc, 1, 1);
     cfg.numAttrs = overlap ? 2u : 1u;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mq, mkh, mv, my, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mq, mkh, mv, my, mm, p);
     *launched = true;
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
@@ -479,7 +489,12 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                     CUtensorMap my;
                     rc = make_map(&my, y, B, L, F, H, 32);
                     bool done = false;
-                    if (rc == FA_B200_OK && use_pair_kernel(H, mask != nullptr, p.q_pairs, sch.tail_steps, flags)) {
+                    // mask tiles through TMA when every mask row starts on a 16-byte boundary; else the
+                    // softmax threads (of the kernel on single CTAs) read their rows straight from global memory
+                    CUtensorMap mm = mq;
+                    p.mask_tma = (mask && mask_rows_aligned(mask, L)) ? 1u : 0u;
+                    if (rc == FA_B200_OK && p.mask_tma) rc = make_mask_map(&mm, mask, B, L);
+                    if (rc == FA_B200_OK && use_pair_kernel(H, !mask || p.mask_tma, p.q_pairs, sch.tail_steps, flags)) {
                         // K as halves of a tile: boxes of 64 keys x 64 columns
                         CUtensorMap mkh;
                         rc = make_map(&mkh, k, B, L, F, H, 64);
@@ -487,16 +502,12 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                             Params pp = p;
                             pp.full_rounds = pp.tail_items = pp.tail_steps = pp.tail_grid = 0;
                             const uint32_t quads = ((p.q_pairs + 1u) / 2u) * p.R * B;
-                            rc = launch_pair(*c, mq, mkh, mv, my, pp, quads, st, overlap, &done);
+                            rc = mask ? launch_pair<true>(*c, mq, mkh, mv, my, mm, pp, quads, st, overlap, &done)
+                                      : launch_pair<false>(*c, mq, mkh, mv, my, mm, pp, quads, st, overlap, &done);
                         }
                     }
                     if (rc == FA_B200_OK && !done) {
                         if (mask) {
-                            // mask tiles through TMA when every mask row starts on a 16-byte boundary; else the
-                            // softmax threads read their rows straight from global memory
-                            CUtensorMap mm = mq;
-                            p.mask_tma = ((L & 7u) == 0u && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0u) ? 1u : 0u;
-                            if (p.mask_tma) rc = make_mask_map(&mm, mask, B, L);
                             if (rc == FA_B200_OK)
                                 rc = H == 128 ? launch_pipelined<128, true>(*c, 10, mq, mk, mv, my, mm, p, sch.grid, st, overlap)
                                               : launch_pipelined<64, true>(*c, 11, mq, mk, mv, my, mm, p, sch.grid, st, overlap);
@@ -976,7 +987,7 @@ int fa_b200_describe_schedule(uint32_t B, uint32_t L, uint32_t F, uint32_t head_
     const Schedule s = make_schedule(n_items, n, sm_count,
                                      (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
     const uint32_t q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
-    if (use_pair_kernel(head_dim, false, q_pairs, s.tail_steps, flags) && sm_count >= 2) {
+    if (use_pair_kernel(head_dim, true, q_pairs, s.tail_steps, flags) && sm_count >= 2) {
         // pairs of CTAs: work items of 512 query rows, one cluster of two CTAs per pair of SMs
         const uint32_t quads = ((q_pairs + 1) / 2) * (F / head_dim) * B, clusters = quads < sm_count / 2 ? quads : sm_count / 2;
         out[0] = 3;
@@ -1010,7 +1021,8 @@ int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
     const uint32_t n = (L + fa::kTile - 1) / fa::kTile, q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
     const Schedule s = make_schedule(q_pairs * (F / head_dim) * B, n, static_cast<uint32_t>(sms),
                                      (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
-    return use_pair_kernel(head_dim, has_mask != 0, q_pairs, s.tail_steps, flags) ? 3 : 2;
+    // (a mask is taken to start on a 16-byte boundary here)
+    return use_pair_kernel(head_dim, !has_mask || (L & 7u) == 0u, q_pairs, s.tail_steps, flags) ? 3 : 2;
 }
 
 }  // extern "C"

@@ -16,29 +16,38 @@
 //     buffer free) is committed once to each CTA's own copy of the barrier;
 //   - tensor memory is allocated and released by both CTAs together, and the two leave together (a cluster
 //     barrier), because the peer's shared and tensor memory are operands of the leader's MMAs to the end.
-// Every CTA loads its own tiles with plain TMA copies.  Work items are whole (no divided last round, no
-// mask): the launcher takes this kernel only for such calls.
+// Every CTA loads its own tiles with plain TMA copies.  Work items are whole (no divided last round): the
+// launcher takes this kernel only for such calls.
+// With a mask (kHasMask; rows of the mask must start on 16-byte boundaries) each CTA also brings in, by TMA
+// and on barriers of its own, the 128 x 128 mask tile of each of its query tiles and every key step, into
+// one buffer per query tile; the softmax threads add their row of it to the scores and hand the buffer
+// back at once, so the next step's tile is on its way while this step's exponentials are taken.  The ring
+// is shorter to make room for the two buffers.
 #pragma once
 
 #include "fa_kernels.cuh"
 
 namespace fa {
 
-struct PairCfg {
+template <bool kHasMask = false>
+struct PairCfgT {
     static constexpr int H = 128;
     using G = TileGeom<128>;
-    static constexpr int kSlots = 8;                        // ring slots of HALF a K or V tile each
+    static constexpr int kSlots = kHasMask ? 4 : 8;         // ring slots of HALF a K or V tile each
     static constexpr int kSlotBytes = G::kTileBytes / 2;    // 16 KiB: 64 keys x 128 columns, or 128 keys x 64 columns
     static constexpr int kQBytes = 2 * G::kTileBytes;       // this CTA's two query tiles
     static constexpr int kRingBytes = kSlots * kSlotBytes;
+    static constexpr int kMaskTileBytes = kTile * kTile * 2;            // 128 x 128 fp16: two boxes of 64 keys
+    static constexpr int kMaskBytes = kHasMask ? 2 * kMaskTileBytes : 0;   // one buffer per query tile
     static constexpr int kStageBytes = 4 * 32 * 128;        // epilogue staging: per warp 32 rows x 64 fp16
-    static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + 1024;   // + alignment slack
+    static constexpr int kSmemBytes = kQBytes + kRingBytes + kMaskBytes + kStageBytes + 1024;   // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
     // tensor memory columns, in each CTA: S [0,128) shared by its two tiles in turn, P0 [128,192), P1 [192,256),
     // O0 [256,384), O1 [384,512)
     static constexpr uint32_t kColS = 0, kColP0 = 128, kColP1 = 192, kColO0 = 256, kColO1 = 384;
     static constexpr int kHeldChunks = 1;
 };
+using PairCfg = PairCfgT<false>;
 
 // S[256 x 128] = Q[256 x 128] K[128 x 128]^T for tile i of both CTAs: A = this CTA's Q tile (two boxes of
 // 128 rows x 64 columns), B = this CTA's half of the K tile (two boxes of 64 keys x 64 columns).
@@ -58,7 +67,7 @@ __device__ __forceinline__ void issue_qk_pair(uint32_t tS, uint32_t sQ, uint32_t
 // head columns of the V tile (one box of 128 keys x 64 columns, MN-major).
 __device__ __forceinline__ void issue_pv_pair(uint32_t tO, uint32_t tP, uint32_t sVhalf, uint32_t accumulate) {
     constexpr uint32_t idesc = make_idesc_f16_pair(128, 1);
-    const uint64_t dv = make_smem_desc<128>(sVhalf, PairCfg::kSlotBytes);
+    const uint64_t dv = make_smem_desc<128>(sVhalf, PairCfg::kSlotBytes);   // (the same in both instances)
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
         mma_ts_pair(tO, tP + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc, (accumulate | ks) ? 1u : 0u);
@@ -68,12 +77,15 @@ __device__ __forceinline__ void issue_pv_pair(uint32_t tO, uint32_t tP, uint32_t
 // (batch, head): n_items = ceil(L / 512) * R * B, numbered row-block fastest; cluster c takes items c,
 // c + clusters, ...  Warp roles as in fa_fwd_pipelined<128>; in the peer CTA the two issuing warps only
 // take part in allocating and releasing tensor memory.
+// tmM is the map of the mask (boxes of 128 rows x 64 keys); instances without a mask get any valid map.
+template <bool kHasMask>
 __global__ void __launch_bounds__(512, 1)
 fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKh,
-            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmY, const Params p) {
+            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmY,
+            const __grid_constant__ CUtensorMap tmM, const Params p) {
     constexpr int H = 128;
     using G = TileGeom<128>;
-    using C = PairCfg;
+    using C = PairCfgT<kHasMask>;
     constexpr int NS = C::kSlots;
     enum {
         BAR_QFULL0 = 0, BAR_QFULL1,  // leader: query tile i of both CTAs landed (bytes of both)
@@ -86,6 +98,8 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         BAR_OFREE0, BAR_OFREE1,      // leader: O of tile i read out in both CTAs (8 warps)
         BAR_OLOCAL0, BAR_OLOCAL1,    // each CTA: O of tile i read out here (4 warps), for its softmax warps
         BAR_FINAL, BAR_FINAL2,       // leader: every MMA of an issuing warp retired
+        BAR_MFULL0, BAR_MFULL1,      // each CTA: the mask tile of its query tile i and this key step landed
+        BAR_MEMPTY0, BAR_MEMPTY1,    // each CTA: that tile has been read by the 4 softmax warps of tile i
         BAR_FULL,                    // leader: NS ring barriers, both halves of a tile landed
         BAR_EMPTY = BAR_FULL + NS,   // each CTA: NS ring barriers, slot free
         BAR_COUNT = BAR_EMPTY + NS
@@ -113,7 +127,8 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;                   // two tiles
     const uint32_t sRing = smem_base + C::kQBytes;   // NS half tiles
-    const uint32_t sStage = sRing + C::kRingBytes;   // epilogue staging, 4 KiB per epilogue warp
+    const uint32_t sMask = sRing + C::kRingBytes;    // two mask tiles (instance with a mask only)
+    const uint32_t sStage = sMask + C::kMaskBytes;   // epilogue staging, 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };                                   // this CTA's copy
     const uint32_t bar0_leader = map_to_cta(bar0, 0), bar0_peer = map_to_cta(bar0, 1);
@@ -126,7 +141,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         for (int i = 0; i < BAR_COUNT; ++i) {
             uint32_t count = 1;
             if (i == BAR_P0 || i == BAR_P1 || i == BAR_SFREE || i == BAR_OFREE0 || i == BAR_OFREE1) count = 8;
-            if (i == BAR_A0 || i == BAR_A1 || i == BAR_OLOCAL0 || i == BAR_OLOCAL1) count = 4;
+            if (i == BAR_A0 || i == BAR_A1 || i == BAR_OLOCAL0 || i == BAR_OLOCAL1 || i == BAR_MEMPTY0 || i == BAR_MEMPTY1) count = 4;
             mbar_init(bar(i), count);
         }
         abort_flag = 0;
@@ -134,6 +149,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmKh);
         prefetch_tensormap(&tmV);
+        if constexpr (kHasMask) prefetch_tensormap(&tmM);
     }
 #ifdef FA_DEBUG
     dbg_begin(p, ctl, smem_base, C::kSmemBytes - 1024);
@@ -188,27 +204,40 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(lbar(BAR_SFREE));
+                if constexpr (kHasMask) {
+                    // this tile's mask tile of this step; its buffer is handed back as soon as it has been read
+                    mbar_wait(bar(BAR_MFULL0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_MFULL0 + i));
+                    add_mask_tile_row(s, sMask + i * C::kMaskTileBytes, row, p.mask_to_score);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(BAR_MEMPTY0 + i));
+                }
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
                 if (first) m = row_max(s);
                 {
+                    // A row that has seen nothing but -inf so far (possible only with a mask) takes 0 as the
+                    // reference of its exponents, so that P = 0 and l = 0 instead of inf - inf.
+                    float nmc = -m * c;
+                    if constexpr (kHasMask) nmc = (m == -INFINITY) ? 0.f : nmc;
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     uint32_t held[16 * C::kHeldChunks];
-                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, -m * c, tP, mx4, held);
+                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, nmc, tP, mx4, held);
                     if (g > 0) {
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                     }
 #pragma unroll
                     for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
-                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, -m * c, tP, mx4);
+                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, nmc, tP, mx4);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
                         const float m_new = moved ? mx : m;
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
                         m = m_new;
+                        float nmc2 = -m * c;
+                        if constexpr (kHasMask) nmc2 = (m == -INFINITY) ? 0.f : nmc2;
                         float unused[4];
-                        l = l * alpha + exp_chunks<0, 4, false>(s, c, -m * c, tP, unused);
+                        l = l * alpha + exp_chunks<0, 4, false>(s, c, nmc2, tP, unused);
                         if (g > 0) mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                         __syncwarp();
@@ -421,6 +450,37 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 // barrier lives in the leader, where the peer cannot poll it: give them a bounded time
                 // (hundreds of times a copy's latency) before the CTA goes on to leave.
                 for (int spin = 0; spin < 200; ++spin) __nanosleep(1000);
+            }
+        } else if (kHasMask && warp == 15 && elect_one()) {
+            // -------------------------------------------------------------- TMA producer of the mask tiles (both CTAs)
+            // Tile i's buffer is filled for key step g as soon as the tile's softmax warps have read step g - 1
+            // out of it.  Boxes that lie beyond the end of the sequence (keys or rows) arrive as zeros.
+            uint32_t g = 0;   // global step
+            bool stop = false;
+            for (uint32_t item = cluster; item < n_items && !stop; item += n_clusters) {
+                const uint32_t q_quad = item % q_quads, bh = item / q_quads;
+                const int32_t batch = static_cast<int32_t>(bh / p.R);
+                const int32_t q_row0 = static_cast<int32_t>((q_quad * 2u + rank) * 2u * kTile);
+                for (uint32_t j = 0; j < n && !stop; ++j, ++g) {
+                    const int32_t key0 = static_cast<int32_t>(j * kTile);
+                    for (uint32_t i = 0; i < 2; ++i) {
+                        if (g > 0 && !mbar_wait(bar(BAR_MEMPTY0 + i), (g - 1u) & 1u, ctl, kRoleProducer | (BAR_MEMPTY0 + i))) {
+                            stop = true;
+                            break;
+                        }
+                        const uint32_t dst = sMask + i * C::kMaskTileBytes;
+                        const int32_t r0 = q_row0 + static_cast<int32_t>(i * kTile);
+                        mbar_expect_tx(bar(BAR_MFULL0 + i), C::kMaskTileBytes);
+                        tma_load_3d(dst, &tmM, bar(BAR_MFULL0 + i), key0, r0, batch);
+                        tma_load_3d(dst + kTile * 128, &tmM, bar(BAR_MFULL0 + i), key0 + 64, r0, batch);
+                    }
+                }
+            }
+            if (abort_flag != 0u && g > 0u) {   // do not leave while the last mask tiles may still be landing
+                const long long t_0 = clock64();
+                while (!(mbar_try_wait(bar(BAR_MFULL0), (g - 1u) & 1u) && mbar_try_wait(bar(BAR_MFULL1), (g - 1u) & 1u)) &&
+                       clock64() - t_0 < 200000000LL) {
+                }
             }
         }
     }

@@ -82,7 +82,9 @@ def test_argument_rejections_happen_before_any_cuda_call(lib):
     assert _call(lib, H=32, flags=_lib.FLAG_FORCE_PIPELINED) == _lib.ERR_FLAGS
     assert _call(lib, H=64, F=64, flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS              # head_dim 128 only
     assert _call(lib, H=128, F=128, flags=_lib.FLAG_FORCE_PAIR | _lib.FLAG_NO_PAIR) == _lib.ERR_FLAGS
-    assert _call(lib, H=128, F=128, mask=_aligned(), flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS
+    # with a mask only when TMA can fetch its tiles: every mask row on a 16-byte boundary
+    assert _call(lib, H=128, F=128, mask=_aligned() + 2, flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS
+    assert _call(lib, H=128, F=128, L=36, mask=_aligned(), flags=_lib.FLAG_FORCE_PAIR) == _lib.ERR_FLAGS
 
 
 def test_host_entry_rejections(lib):
@@ -97,6 +99,8 @@ def test_kernel_selection(lib):
     sel = lib.fa_b200_select_kernel
     assert sel(4, 2048, 4096, 128, 0, 0) == 3      # headline: pipelined, on pairs of CTAs
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_NO_PAIR) == 2
+    assert sel(4, 2048, 4096, 128, 1, 0) == 3      # with a mask too, its rows being 16-byte aligned
+    assert sel(4, 2044, 4096, 128, 1, 0) == 2      # mask rows that TMA cannot fetch: single CTAs
     assert sel(1, 16384, 4096, 128, 0, 0) == 3
     assert sel(1, 16384, 512, 128, 0, 0) == 2      # the last round of this one is divided: single CTAs
     assert sel(4, 2048 + 256, 4096, 128, 0, 0) == 2    # nine 256-row blocks: an odd one would idle half a pair

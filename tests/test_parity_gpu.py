@@ -420,7 +420,8 @@ def test_additive_mask(H, L):
     mask[1, :, L - L // 3:] = float("-inf")                                        # padding
     mask[1, :, : L // 2] += 0.5 * torch.randn(L, L // 2, generator=torch.Generator().manual_seed(1)).half()
     expected = oracle(q, k, v, H, mask)
-    for flags in [f for f in kernels_for(H) if f != PAIR]:     # the kernel on pairs of CTAs takes no mask
+    # the kernel on pairs of CTAs takes a mask only through TMA: rows of 16-byte multiples
+    for flags in [f for f in kernels_for(H) if f != PAIR or L % 8 == 0]:
         assert_close(run(q, k, v, H, mask=mask, flags=flags), expected)
 
 
@@ -448,9 +449,10 @@ def test_additive_mask_rows_at_any_alignment(L):
 
 @pytest.mark.parametrize("B,R,L,H", [(2, 8, 2048, 128), (2, 8, 2048, 64), (4, 32, 2048, 128), (1, 3, 1000, 128), (3, 4, 1336, 64)])
 def test_additive_mask_on_long_sequences(B, R, L, H):
-    """The warp-specialised kernel brings the mask in tile by tile through TMA into one buffer that the two query
-    tiles of a CTA use in turn; many key steps and many work items per CTA, where the two tiles drift apart in
-    time.  Causal mask plus a soft random part; against fp32 attention with the mask on the same GPU."""
+    """The warp-specialised kernels bring the mask in tile by tile through TMA (on single CTAs into one buffer that
+    the two query tiles use in turn, on pairs of CTAs into a buffer per query tile); many key steps and many work
+    items per CTA, where the two tiles drift apart in time.  Causal mask plus a soft random part; against fp32
+    attention with the mask on the same GPU, and the two kernels against each other bit for bit."""
     g = torch.Generator(device="cuda")
     g.manual_seed(L + H)
     q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() * 0.5 for _ in range(3))
@@ -460,6 +462,10 @@ def test_additive_mask_on_long_sequences(B, R, L, H):
     y = fa.attention_forward(H, 32, q, k, v, mask, flags=ONE | _lib.FLAG_SYNC)
     y2 = fa.attention_forward(H, 32, q, k, v, mask, flags=ONE | _lib.FLAG_SYNC)
     assert torch.equal(y, y2) and torch.isfinite(y).all()
+    if H == 128:
+        for flags in (PAIR, 0):
+            yp = fa.attention_forward(H, 32, q, k, v, mask, flags=flags | _lib.FLAG_SYNC | _lib.FLAG_NO_SPLIT)
+            assert torch.equal(yp, y), flags
     qf, kf, vf = (t.float().view(B, L, R, H).transpose(1, 2) for t in (q, k, v))
     ref = (torch.softmax(qf @ kf.mT / H ** 0.5 + mask.float()[:, None], -1) @ vf).transpose(1, 2).reshape(B, L, R * H)
     d = (y.float() - ref).abs()
@@ -662,7 +668,7 @@ def test_checked_build_refuses_bad_operands_without_touching_memory():
 @pytest.mark.parametrize("H,B,R,L,flags,masked", [
     (16, 2, 3, 200, SIMPLE, False), (64, 2, 3, 300, SIMPLE, True), (64, 3, 5, 700, ONE, False), (64, 2, 2, 520, ONE, True),
     (128, 2, 3, 1000, ONE, False), (128, 2, 4, 2048, PAIR, False), (128, 1, 4, 2048 + 77, 0, False), (128, 1, 2, 650, ONE, True),
-    (128, 20, 10, 300, PAIR, False)])
+    (128, 20, 10, 300, PAIR, False), (128, 2, 3, 1000, PAIR, True), (128, 3, 4, 2048, PAIR, True)])
 def test_checked_build_runs_clean_and_gives_the_same_bits(H, B, R, L, flags, masked):
     """Every kernel under the checked build: each TMA copy and tensor-memory access is checked against the
     CTA's tile area, the tensor's extent and the CTA's tensor-memory allocation, tile buffers and Y are
@@ -780,7 +786,7 @@ def test_mask_against_the_reference_kernel_single_chunk(H, C):
     y_ref = _run_ref_wmma(lib, q, k, v, H, C, dmask)
     err_ref = error_metrics(y_ref.float().cpu(), expected)
     assert err_ref["max_abs"] <= 1e-2, err_ref       # the reference kernel and the oracle formula mean the same mask
-    for flags in [f for f in kernels_for(H) if f != PAIR]:
+    for flags in kernels_for(H):
         y = fa.attention_forward(H, C, q, k, v, dmask, flags=flags | _lib.FLAG_SYNC)
         torch.testing.assert_close(y.float(), y_ref.float(), rtol=0.01, atol=0.01)
         assert_close(y.float().cpu(), expected)
