@@ -4,10 +4,12 @@
 //   fa_fwd_simple<H, kHasMask>  one 128-row query tile per CTA, 128 threads, every step in program
 //                               order.  Covers every head_dim (16, 32, 64, 128), the additive mask
 //                               and tiny problems; several CTAs per SM overlap one another.
-//   fa_fwd_pipelined<H>         two 128-row query tiles per CTA, 512 threads split into roles
-//                               (2 softmax warpgroups, 1 epilogue warpgroup, 1 MMA warp, 1 TMA
-//                               warp); K/V stream through a shared-memory ring; the softmax of one
-//                               tile overlaps the MMAs of the other.  H in {64, 128}, no mask.
+//   fa_fwd_pipelined<H, kHasMask>  two 128-row query tiles per CTA, 512 threads split into roles
+//                               (2 softmax warpgroups, 1 epilogue warpgroup, 1 or 2 MMA warps, 1 TMA
+//                               warp, 1 warp for the mask tiles); K/V stream through a shared-memory
+//                               ring; the softmax of one tile overlaps the MMAs of the other.
+//                               H in {64, 128}.
+// fa_pair.cuh holds a third, fa_fwd_pair<kHasMask>: the same roles on pairs of CTAs at H = 128.
 //
 // What they replace in the reference (include/fused_attn.cuh): attention_kernel (605-858) and the
 // threadblock_* primitives it calls (48-521).  The maths is the reference's blockwise merge of

@@ -54,7 +54,9 @@ enum {
                                           while the previous kernel of the stream drains; they touch
                                           global memory only once that kernel has completed, so the
                                           stream's ordering guarantees are unchanged             */
-    FA_B200_FLAG_FORCE_PAIR = 32u,     /* head_dim 128, no mask: always use the kernel that runs on pairs
+    FA_B200_FLAG_FORCE_PAIR = 32u,     /* head_dim 128 (with a mask: one whose rows all start on 16-byte
+                                          boundaries, else FA_B200_ERR_FLAGS): always use the kernel
+                                          that runs on pairs
                                           of CTAs (one MMA of 256 rows for two SMs); implies whole work
                                           items.  By default it is taken for such calls when their last
                                           round is not divided and the sequence has an even or large
@@ -193,7 +195,8 @@ int fa_b200_selftest_debug_checks(int device, uint32_t out[4]);
 /*
  * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
  * kernel, 2 for the warp-specialised kernel, 3 for the warp-specialised kernel on pairs of CTAs
- * (head_dim 128, no mask, whole work items), negative status on invalid arguments.
+ * (head_dim 128, whole work items; a mask is taken to start on a 16-byte boundary, its rows then
+ * do so whenever L is a multiple of 8), negative status on invalid arguments.
  * No counterpart in the reference.
  */
 int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,

@@ -110,7 +110,6 @@ def test_kernel_selection(lib):
     assert sel(1, 2048, 512, 128, 0, 0) == 2       # 32 items only, but 16 key steps each: pipelined (divided)
     assert sel(1, 512, 512, 128, 0, 0) == 1        # 8 items of 4 key steps cannot occupy the SMs
     assert sel(4, 2048, 512, 16, 0, 0) == 1        # small head_dim
-    assert sel(4, 2048, 4096, 128, 1, 0) == 2      # with a mask: pipelined on single CTAs
     assert sel(4, 2048, 512, 32, 1, 0) == 1
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_FORCE_SIMPLE) == 1
     assert sel(1, 256, 256, 64, 0, _lib.FLAG_FORCE_PIPELINED) == 2
