@@ -572,11 +572,16 @@ struct PipeCfg {
     using G = TileGeom<H>;
     // ring slots of one K or V tile each; with a mask a quarter of the ring makes room for one mask tile
     static constexpr int kStages = (H == 128 ? 4 : 8) * (kHasMask ? 3 : 4) / 4;
+    // Buffers for the two query tiles of a segment.  With two of them (H = 64, where they fit) the next segment's
+    // query tiles, and behind them its K and V tiles, are on their way while this segment still multiplies: the
+    // producer no longer stops at every segment boundary until the last Q K^T has let go of the one buffer.
+    // Shapes of few key steps per segment (short sequences) gain most.
+    static constexpr int kQBufs = H == 64 ? 2 : 1;
     static constexpr int kQBytes = 2 * G::kTileBytes;  // two query tiles
     static constexpr int kRingBytes = kStages * G::kTileBytes;
     static constexpr int kMaskBytes = kHasMask ? kTile * kTile * 2 : 0;   // one 128 x 128 fp16 mask tile (two boxes of 64 keys)
     static constexpr int kStageBytes = 4 * 32 * 128;   // epilogue staging: per warp 32 rows x 64 fp16
-    static constexpr int kSmemBytes = kQBytes + kRingBytes + kMaskBytes + kStageBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kQBufs * kQBytes + kRingBytes + kMaskBytes + kStageBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTmemCols = 512;
     // TMEM columns.  P (fp16, 64 columns per tile) has columns of its own instead of overwriting its
     // S: the next Q K^T of a tile then does not have to wait for the P V that reads P, only for the
@@ -969,7 +974,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         BAR_MEMPTY0, BAR_MEMPTY1,    // softmax of tile i -> TMA: the mask tile has been read (4 arrivals)
         BAR_FINAL,                   // MMA -> itself: every MMA retired
         BAR_FINAL2,                  // the same for the second issuing warp
-        BAR_FULL,                    // NS ring barriers TMA -> MMA
+        BAR_QB,                      // QFULL0, QFULL1, QEMPTY0, QEMPTY1 of the second query buffer (H = 64)
+        BAR_FULL = BAR_QB + 4,       // NS ring barriers TMA -> MMA
         BAR_EMPTY = BAR_FULL + NS,   // NS ring barriers MMA -> TMA
         BAR_COUNT = BAR_EMPTY + NS
     };
@@ -993,12 +999,18 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     volatile Plan& pl_s = plan_smem;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sQ = smem_base;                   // two tiles
-    const uint32_t sRing = smem_base + C::kQBytes;   // NS tiles
+    const uint32_t sQ = smem_base;                   // two tiles per buffer
+    const uint32_t sRing = smem_base + C::kQBufs * C::kQBytes;   // NS tiles
     const uint32_t sMask = sRing + C::kRingBytes;    // one mask tile (instances with a mask only)
     const uint32_t sStage = sMask + C::kMaskBytes;   // epilogue staging, 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
+    // Segment k's query tiles: buffer k mod kQBufs; its barriers complete one phase per use of that buffer.
+    auto q_addr = [&](uint32_t k, uint32_t i) { return sQ + (k % C::kQBufs) * C::kQBytes + i * G::kTileBytes; };
+    auto q_phase = [&](uint32_t k) { return (k / C::kQBufs) & 1u; };
+    auto bar_qfull = [&](uint32_t k, uint32_t i) { return bar(((k % C::kQBufs) ? BAR_QB : BAR_QFULL0) + i); };
+    auto bar_qempty = [&](uint32_t k, uint32_t i) { return bar(((k % C::kQBufs) ? BAR_QB + 2 : BAR_QEMPTY0) + i); };
+    auto code_qfull = [&](uint32_t k, uint32_t i) { return static_cast<uint32_t>(((k % C::kQBufs) ? BAR_QB : BAR_QFULL0) + i); };
     const WaitCtl ctl{p.status, &abort_flag, kWaitCapCycles, p.status + 2, p.launch_id};
 
     if (tid == 13 * 32) {
@@ -1401,22 +1413,22 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             uint32_t k = 0, j = 0, len = seg_len(pl, p, 0);
             if (steps > 0 && warp == 12) {
                 // S tiles of the very first step
-                mwait(bar(BAR_QFULL0), 0, BAR_QFULL0);
+                mwait(bar_qfull(0, 0), 0, code_qfull(0, 0));
                 wait_full(0);
                 tc_fence_after();
                 if (leader && ok) {
-                    issue_qk<H>(tS0, sQ, slot_addr(0));
+                    issue_qk<H>(tS0, q_addr(0, 0), slot_addr(0));
                     tc_commit(bar(BAR_S0));
-                    if (len == 1) tc_commit(bar(BAR_QEMPTY0));
+                    if (len == 1) tc_commit(bar_qempty(0, 0));
                 }
-                mwait(bar(BAR_QFULL1), 0, BAR_QFULL1);
+                mwait(bar_qfull(0, 1), 0, code_qfull(0, 1));
                 // one S buffer for both tiles: tile 0's scores must have been read first
                 if constexpr (C::kSharedS) mwait(bar(BAR_SFREE0), 0, BAR_SFREE0);
                 tc_fence_after();
                 if (leader && ok) {
-                    issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(0));
+                    issue_qk<H>(tS1, q_addr(0, 1), slot_addr(0));
                     tc_commit(bar(BAR_S1));
-                    if (len == 1) tc_commit(bar(BAR_QEMPTY1));
+                    if (len == 1) tc_commit(bar_qempty(0, 1));
                     free_slot(0);
                 }
             }
@@ -1434,17 +1446,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const bool last_of_seg = j + 1 == len;   // a segment's last Q K^T is its last use of the query tile
                         const uint32_t tk = 2 * q;
                         if (!(polled && mbar_poll_end<0>())) wait_full(tk);
-                        if (new_seg) mwait(bar(BAR_QFULL0), k & 1u, BAR_QFULL0);
+                        if (new_seg) mwait(bar_qfull(k, 0), q_phase(k), code_qfull(k, 0));
                         // With one S buffer its uses are numbered 2q + i (tile i, step q) and use u
                         // needs the reading of use u - 1 (one barrier, phase = use).
                         mwait(bar(BAR_SFREE0), 1u, BAR_SFREE0);
                         tc_fence_after();
                         if (leader && ok) {
-                            issue_qk<H>(tS0, sQ, slot_addr(tk));
+                            issue_qk<H>(tS0, q_addr(k, 0), slot_addr(tk));
                             tc_commit(bar(BAR_S0));
-                            if (last_of_seg) tc_commit(bar(BAR_QEMPTY0));
+                            if (last_of_seg) tc_commit(bar_qempty(k, 0));
                         }
-                        if (new_seg) mwait(bar(BAR_QFULL1), k & 1u, BAR_QFULL1);
+                        if (new_seg) mwait(bar_qfull(k, 1), q_phase(k), code_qfull(k, 1));
                         mwait(bar(BAR_SFREE0), 0u, BAR_SFREE0);
                         tc_fence_after();
                         polled = q + 1 < steps;
@@ -1453,9 +1465,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             mbar_poll_begin<0>(bar(BAR_FULL + (nk % NS)), (nk / NS) & 1u);
                         }
                         if (leader && ok) {
-                            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                            issue_qk<H>(tS1, q_addr(k, 1), slot_addr(tk));
                             tc_commit(bar(BAR_S1));
-                            if (last_of_seg) tc_commit(bar(BAR_QEMPTY1));
+                            if (last_of_seg) tc_commit(bar_qempty(k, 1));
                             free_slot(tk);
                         }
                     }
@@ -1503,6 +1515,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     // is the next step the last of its segment (its Q K^T the last use of the query tile)?
                     const bool next_last_of_seg = next_new_seg ? seg_len(pl, p, k + 1u) == 1u : j + 2 == len;
                     const uint32_t acc = j > 0 ? 1u : 0u;
+                    const uint32_t kn = next_new_seg ? k + 1u : k;   // the segment of the next step
                     {
                         uint32_t ok_v = 0, ok_k = 0, ok_s0 = 0;
                         if (polled) {
@@ -1513,7 +1526,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         if (!ok_v) wait_full(tv);
                         if (more) {
                             if (!ok_k) wait_full(tk);
-                            if (next_new_seg) mwait(bar(BAR_QFULL0), (k + 1u) & 1u, BAR_QFULL0);
+                            if (next_new_seg) mwait(bar_qfull(kn, 0), q_phase(kn), code_qfull(kn, 0));
                             if (!ok_s0) mwait(bar(BAR_SFREE0), g & 1u, BAR_SFREE0);
                         }
                     }
@@ -1522,9 +1535,9 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (more) {
                         tc_fence_after();
                         if (leader && ok) {
-                            issue_qk<H>(tS0, sQ, slot_addr(tk));
+                            issue_qk<H>(tS0, q_addr(kn, 0), slot_addr(tk));
                             tc_commit(bar(BAR_S0));
-                            if (next_last_of_seg) tc_commit(bar(BAR_QEMPTY0));
+                            if (next_last_of_seg) tc_commit(bar_qempty(kn, 0));
                         }
                     }
                     mwait(bar(BAR_P0), g & 1u, BAR_P0);
@@ -1535,15 +1548,15 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         tc_commit(bar(BAR_PV0));
                     }
                     // tile 1
-                    if (more && next_new_seg) mwait(bar(BAR_QFULL1), (k + 1u) & 1u, BAR_QFULL1);
+                    if (more && next_new_seg) mwait(bar_qfull(kn, 1), q_phase(kn), code_qfull(kn, 1));
                     if (j == 0 && k > 0) mwait(bar(BAR_OFREE1), (k - 1u) & 1u, BAR_OFREE1);
                     if (more) {
                         if (!mbar_poll_end<3>()) mwait(bar(BAR_SFREE1), g & 1u, BAR_SFREE1);
                         tc_fence_after();
                         if (leader && ok) {
-                            issue_qk<H>(tS1, sQ + G::kTileBytes, slot_addr(tk));
+                            issue_qk<H>(tS1, q_addr(kn, 1), slot_addr(tk));
                             tc_commit(bar(BAR_S1));
-                            if (next_last_of_seg) tc_commit(bar(BAR_QEMPTY1));
+                            if (next_last_of_seg) tc_commit(bar_qempty(kn, 1));
                             free_slot(tk);
                         }
                     }
@@ -1576,7 +1589,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             uint32_t t = 0;           // ring item
             uint32_t k = 0;           // segment
             bool stop = false;
-            bool q_pending[2] = {false, false};
+            uint32_t q_asked[2] = {0, 0};   // for how many segments query tile tt has been asked for
             for (; k < nseg && !stop; ++k) {
                 const Seg sg = get_seg(pl_s, t0, p, k);
 #ifdef FA_DEBUG
@@ -1590,12 +1603,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int32_t q_row0 = static_cast<int32_t>(q_pair * 2u * kTile);
                 for (uint32_t tt = 0; tt < 2 * sg.len; ++tt, ++t) {
                     if (tt < 2) {
-                        // query tile tt of this segment, once the previous one has let go of the buffer
-                        if (k > 0 && !mbar_wait(bar(BAR_QEMPTY0 + tt), (k - 1u) & 1u, ctl,
-                                                kRoleProducer | (BAR_QEMPTY0 + tt))) { stop = true; break; }
-                        load_tile<H>(sQ + tt * G::kTileBytes, &tmQ, bar(BAR_QFULL0 + tt), col0,
+                        // query tile tt of this segment, once the buffer's previous user has let go of it
+                        if (k >= static_cast<uint32_t>(C::kQBufs) &&
+                            !mbar_wait(bar_qempty(k, tt), q_phase(k - C::kQBufs), ctl,
+                                       kRoleProducer | (BAR_QEMPTY0 + tt))) { stop = true; break; }
+                        load_tile<H>(q_addr(k, tt), &tmQ, bar_qfull(k, tt), col0,
                                      q_row0 + static_cast<int32_t>(tt * kTile), batch);
-                        q_pending[tt] = true;
+                        q_asked[tt] = k + 1u;
                     }
                     const uint32_t slot = t % NS;
                     if (!mbar_wait(bar(BAR_EMPTY + slot), ((t / NS) & 1u) ^ 1u, ctl,
@@ -1613,10 +1627,13 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                            clock64() - t0 < 200000000LL) {
                     }
                 }
+                // the query tiles asked for last (with two buffers, those of the last two segments)
                 for (uint32_t tt = 0; tt < 2; ++tt) {
-                    const long long t0 = clock64();
-                    while (q_pending[tt] && !mbar_try_wait(bar(BAR_QFULL0 + tt), (k > 0 ? k - 1u : 0u) & 1u) &&
-                           clock64() - t0 < 200000000LL) {
+                    const uint32_t first_q = q_asked[tt] > static_cast<uint32_t>(C::kQBufs) ? q_asked[tt] - C::kQBufs : 0u;
+                    for (uint32_t kk = first_q; kk < q_asked[tt]; ++kk) {
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(bar_qfull(kk, tt), q_phase(kk)) && clock64() - t0 < 200000000LL) {
+                        }
                     }
                 }
             }
