@@ -5,8 +5,9 @@
 
   bin/fa_b200_driver  torch-free C++ program over the C ABI (fill, run, check, time)
 
-Run ``python -m fused_attention_b200.build [--ext] [--driver] [--debug]`` (``--debug`` also builds the checked
-library ``lib/libfa_b200_debug.so``).  Nothing is installed outside the tree.
+Run ``python -m fused_attention_b200.build [--ext] [--driver] [--debug] [--cycles]`` (``--debug`` also builds the
+checked library ``lib/libfa_b200_debug.so``, ``--cycles`` the clock-counting one ``lib/libfa_b200_cycles.so``).
+Nothing is installed outside the tree.
 """
 from __future__ import annotations
 
@@ -23,6 +24,7 @@ LIBDIR = os.path.join(HERE, "lib")
 EXTDIR = os.path.join(HERE, "ext")
 LIB = os.path.join(LIBDIR, "libfa_b200.so")
 DEBUG_LIB = os.path.join(LIBDIR, "libfa_b200_debug.so")   # the checked build (-DFA_DEBUG), used by one GPU test
+CYCLES_LIB = os.path.join(LIBDIR, "libfa_b200_cycles.so")  # the clock-counting build (-DFA_CYCLES), see cycles.py
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,18 +51,22 @@ def lib_sources() -> list[str]:
         os.path.join(ROOT, "include", "fa_b200.h")]
 
 
-def build_lib(force: bool = False, verbose: bool = False, debug: bool = False) -> str:
+def build_lib(force: bool = False, verbose: bool = False, debug: bool = False, cycles: bool = False) -> str:
     """Compile csrc/fa_b200.cu into lib/libfa_b200.so (cross-compiles without a GPU).
 
     ``debug`` builds lib/libfa_b200_debug.so instead, with -DFA_DEBUG: every TMA copy and tensor-memory
-    access checks its operands first (see the checked-build section of csrc/fa_ptx.cuh)."""
+    access checks its operands first (see the checked-build section of csrc/fa_ptx.cuh).
+    ``cycles`` builds lib/libfa_b200_cycles.so, with -DFA_CYCLES: CTA 0 of the warp-specialised kernels
+    records time stamps and its SM clock count per launch (read by cycles.py)."""
     os.makedirs(LIBDIR, exist_ok=True)
-    out = DEBUG_LIB if debug else LIB
+    out = DEBUG_LIB if debug else (CYCLES_LIB if cycles else LIB)
     if not force and not _stale(out, lib_sources()):
         return out
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if debug:
         cmd += ["-DFA_DEBUG"]
+    elif cycles:
+        cmd += ["-DFA_CYCLES"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", out, os.path.join(CSRC, "fa_b200.cu")]
@@ -123,6 +129,8 @@ def main(argv: list[str]) -> int:
     print(build_lib(force=force, verbose="-v" in argv))
     if "--debug" in argv:
         print(build_lib(force=force, verbose="-v" in argv, debug=True))
+    if "--cycles" in argv:
+        print(build_lib(force=force, verbose="-v" in argv, cycles=True))
     if "--ext" in argv:
         print(build_ext(force=force))
     if "--driver" in argv:

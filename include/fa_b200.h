@@ -192,6 +192,17 @@ int fa_b200_selftest_bounded_wait(int device, uint32_t out[3]);
  */
 int fa_b200_selftest_debug_checks(int device, uint32_t out[4]);
 
+#ifdef FA_CYCLES
+/*
+ * Only in the clock-counting build of the library (compiled with -DFA_CYCLES): from now on CTA 0 of the
+ * warp-specialised kernels writes, per launch, four 64-bit words into record (launch id mod 64) of the
+ * given device buffer of 256 words: the global timer (ns) at its entry, after its wait for the previous
+ * kernel of the stream and at its end, and its SM clock count between the last two.  NULL stops the
+ * recording.  The buffer must outlive the launches.  No counterpart in the reference.
+ */
+int fa_b200_debug_cycles(void* device_buffer_of_256_u64);
+#endif
+
 /*
  * Which kernel the default heuristics pick for a shape: returns 1 for the one-tile-per-CTA
  * kernel, 2 for the warp-specialised kernel, 3 for the warp-specialised kernel on pairs of CTAs

@@ -20,10 +20,21 @@ def _header(repo_root):
 
 
 def test_library_exports_every_declared_symbol(lib, repo_root):
-    declared = set(re.findall(r"\b(fa_b200_\w+)\s*\(", _header(repo_root)))
+    text = _header(repo_root)
+    # what the header declares only for a variant build (#ifdef FA_CYCLES ... #endif) is that variant's
+    variant = "".join(re.findall(r"#ifdef FA_CYCLES\n(.*?)#endif", text, flags=re.S))
+    only_variant = set(re.findall(r"\b(fa_b200_\w+)\s*\(", variant))
+    declared = set(re.findall(r"\b(fa_b200_\w+)\s*\(", text)) - only_variant
     assert declared == set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert getattr(lib, name) is not None
+    assert only_variant == {"fa_b200_debug_cycles"}
+    from fused_attention_b200 import build
+    if os.path.exists(build.CYCLES_LIB):
+        import ctypes
+        variant_lib = ctypes.CDLL(build.CYCLES_LIB)
+        for name in declared | only_variant:
+            assert getattr(variant_lib, name) is not None
 
 
 def test_python_constants_match_header(repo_root):

@@ -146,3 +146,21 @@ def test_headline_shards_are_divided_as_designed():
     assert (few["grid"], few["full_rounds"], few["tail_items"], few["tail_grid"]) == (64, 0, 32, 64)
     long = fa.describe_schedule(1, 16384, 4 * 128, 128)   # 256 items of 128 key steps: the last 108 are divided
     assert (long["full_rounds"], long["tail_items"], long["tail_grid"]) == (1, 108, 148)
+
+
+def test_clock_count_records_are_parsed_and_summarised():
+    """fused_attention_b200/cycles.py on a synthetic device buffer: records of launches in any slot order, empty
+    slots skipped, medians of SM clocks, busy time, period and the gap between launches."""
+    from fused_attention_b200 import cycles
+    words = [0] * 256
+    t0 = 1_000_000
+    for n, slot in enumerate((5, 6, 7, 3)):        # launch ids wrap around the 64 records
+        entry = t0 + n * 200_000
+        words[4 * slot: 4 * slot + 4] = [entry, entry + 30_000, entry + 190_000, 300_000 + n]
+    words[4 * 9: 4 * 9 + 4] = [77, 50, 60, 1]      # ready before entry: not a record
+    recs = cycles.parse_records(words)
+    assert [r["sm_clocks"] for r in recs] == [300_000, 300_001, 300_002, 300_003]
+    s = cycles.summarise(recs)
+    assert s["launches"] == 4 and s["sm_clocks"] == 300_002
+    assert s["busy_us"] == 160.0 and s["period_us"] == 200.0 and s["gap_us"] == 40.0
+    assert cycles.summarise([])["sm_clocks"] is None

@@ -691,6 +691,20 @@ def test_checked_build_runs_clean_and_gives_the_same_bits(H, B, R, L, flags, mas
     assert torch.equal(y, fa.attention_forward(H, 16 if H < 128 else 32, q, k, v, mask, flags=flags | _lib.FLAG_SYNC))
 
 
+@pytest.mark.parametrize("flags", [ONE, PAIR])
+def test_clock_counting_build_reports_a_launch(flags):
+    """The -DFA_CYCLES build (fused_attention_b200/cycles.py): CTA 0's time stamps are in order, its busy time is
+    most of the period of back-to-back launches, and its SM clock count over that time is a clock a B200 can run at."""
+    from fused_attention_b200 import build, cycles
+    if not os.path.exists(build.CYCLES_LIB):
+        pytest.skip("clock-counting library not built (python -m fused_attention_b200.build --cycles)")
+    s = cycles.measure(2, 16, 2048, 128, flags=flags, launches=30)
+    assert s["launches"] >= 20, s
+    assert 0.5 * s["period_us"] <= s["busy_us"] <= s["period_us"], s
+    mhz = s["sm_clocks"] / s["busy_us"]
+    assert 900.0 <= mhz <= 2100.0, (mhz, s)
+
+
 # ---------------------------------------------------------------- drop-in module `fused_attn`
 def _fused_attn_module():
     ext_dir = os.path.join(os.path.dirname(fa.__file__), "ext")
