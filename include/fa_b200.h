@@ -132,8 +132,8 @@ int fa_b200_attention_forward_host(const void* q, const void* k, const void* v,
  *     stream order, ahead of its kernel) and the array otherwise keeps what the last call left;
  *     two calls whose kernels overlap on the GPU (different streams) race on it, so serialise them;
  *   - the first call on a device looks up the array's device address and sets the kernel's
- *     shared-memory attribute; make that first call before any stream capture begins.  Calls on
- *     different devices do not wait for one another.
+ *     shared-memory attribute, two calls into the CUDA runtime that later calls do not make.
+ *     Calls on different devices do not wait for one another.
  * flags: 0 or FA_B200_FLAG_SYNC (synchronise the stream and return FA_B200_ERR_DEVICE_TIMEOUT if
  * any CTA reported).  Inputs, outputs, head_dim, chunk_hint, mask: as fa_b200_attention_forward.
  */
