@@ -1644,6 +1644,7 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // follows tile 1 of step g - 1.  Boxes that lie beyond the end of the sequence (keys or rows) arrive
             // as zeros.
             uint32_t g = 0;   // global step
+            uint32_t asked[2] = {0, 0};   // for how many key steps tile i's mask tile has been asked for
             bool stop = false;
             for (uint32_t k = 0; k < nseg && !stop; ++k) {
                 const Seg sg = get_seg(pl_s, t0, p, k);
@@ -1663,13 +1664,16 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         tma_load_3d(sMask, &tmM, bar(BAR_MFULL0 + i), key0, q_row0 + static_cast<int32_t>(i * kTile), batch);
                         tma_load_3d(sMask + kTile * 128, &tmM, bar(BAR_MFULL0 + i), key0 + 64,
                                     q_row0 + static_cast<int32_t>(i * kTile), batch);
+                        asked[i] = g + 1u;
                     }
                 }
             }
-            if (abort_flag != 0u && g > 0u) {   // do not leave while the last mask tiles may still be landing
-                const long long t_0 = clock64();
-                while (!(mbar_try_wait(bar(BAR_MFULL0), (g - 1u) & 1u) && mbar_try_wait(bar(BAR_MFULL1), (g - 1u) & 1u)) &&
-                       clock64() - t_0 < 200000000LL) {
+            if (abort_flag != 0u) {   // do not leave while the mask tiles asked for last may still be landing
+                for (uint32_t i = 0; i < 2; ++i) {
+                    const long long t_0 = clock64();
+                    while (asked[i] > 0u && !mbar_try_wait(bar(BAR_MFULL0 + i), (asked[i] - 1u) & 1u) &&
+                           clock64() - t_0 < 200000000LL) {
+                    }
                 }
             }
         }

@@ -456,6 +456,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // Tile i's buffer is filled for key step g as soon as the tile's softmax warps have read step g - 1
             // out of it.  Boxes that lie beyond the end of the sequence (keys or rows) arrive as zeros.
             uint32_t g = 0;   // global step
+            uint32_t asked[2] = {0, 0};   // for how many key steps tile i's mask tile has been asked for
             bool stop = false;
             for (uint32_t item = cluster; item < n_items && !stop; item += n_clusters) {
                 const uint32_t q_quad = item % q_quads, bh = item / q_quads;
@@ -473,13 +474,16 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                         mbar_expect_tx(bar(BAR_MFULL0 + i), C::kMaskTileBytes);
                         tma_load_3d(dst, &tmM, bar(BAR_MFULL0 + i), key0, r0, batch);
                         tma_load_3d(dst + kTile * 128, &tmM, bar(BAR_MFULL0 + i), key0 + 64, r0, batch);
+                        asked[i] = g + 1u;
                     }
                 }
             }
-            if (abort_flag != 0u && g > 0u) {   // do not leave while the last mask tiles may still be landing
-                const long long t_0 = clock64();
-                while (!(mbar_try_wait(bar(BAR_MFULL0), (g - 1u) & 1u) && mbar_try_wait(bar(BAR_MFULL1), (g - 1u) & 1u)) &&
-                       clock64() - t_0 < 200000000LL) {
+            if (abort_flag != 0u) {   // do not leave while the mask tiles asked for last may still be landing
+                for (uint32_t i = 0; i < 2; ++i) {
+                    const long long t_0 = clock64();
+                    while (asked[i] > 0u && !mbar_try_wait(bar(BAR_MFULL0 + i), (asked[i] - 1u) & 1u) &&
+                           clock64() - t_0 < 200000000LL) {
+                    }
                 }
             }
         }
