@@ -233,13 +233,15 @@ def device_copies(torch, tensors, dev, min_bytes: int, max_copies: int = 64):
 def time_launches(torch, fa, H, chunk, bufs, steps: int, warmup: int, flags: int = 0):
     """Milliseconds per launch of `steps` back-to-back launches (CUDA events on the launching stream)."""
     n = len(bufs)
+    out = torch.empty_like(bufs[0][0])
+    calls = [fa.bind_forward(H, chunk, *b, out=out, flags=flags)[0] for b in bufs]   # arguments checked once
     for i in range(warmup):
-        fa.attention_forward(H, chunk, *bufs[i % n], flags=flags)
+        calls[i % n]()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
     for i in range(steps):
-        fa.attention_forward(H, chunk, *bufs[i % n], flags=flags)
+        calls[i % n]()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
@@ -251,6 +253,8 @@ def sustained_loop(torch, fa, H, chunk, bufs, flops_per_launch: float, ms_guess:
     all the while: what the kernel sustains once the GPU has been loaded for a while, and how the time per
     launch moves with the clock (time x clock = SM kilo-cycles per launch, which does not depend on it)."""
     n = len(bufs)
+    y_out = torch.empty_like(bufs[0][0])
+    calls = [fa.bind_forward(H, chunk, *b, out=y_out)[0] for b in bufs]
     spans = max(5, int(math.ceil(seconds / (span * ms_guess * 1e-3))))
     events = [torch.cuda.Event(enable_timing=True) for _ in range(spans + 1)]
     sampler = ClockSampler(local_rank)
@@ -260,7 +264,7 @@ def sustained_loop(torch, fa, H, chunk, bufs, flops_per_launch: float, ms_guess:
     i = 0
     for s in range(spans):
         for _ in range(span):
-            fa.attention_forward(H, chunk, *bufs[i % n])
+            calls[i % n]()
             i += 1
         events[s + 1].record()
     while not events[-1].query():
@@ -388,8 +392,12 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
         my_flops = fa.attention_flops(shard.b1 - shard.b0, shard.h1 - shard.h0, w.L, w.H)
         host = workload_inputs(w_rank, heads=slice(shard.h0, shard.h1), batches=slice(shard.b0, shard.b1), pin=True)
         bufs, nbuf, one = device_copies(torch, host, dev, 4 * L2_BYTES)
+        # one pass of the hot path = one call of fa_b200_attention_forward; the Python-side checks and the
+        # allocation of the output are done once, outside the timed region (a shard's launch at N = 8 is 30 us)
+        y_out = torch.empty_like(bufs[0][0])
+        calls = [fa.bind_forward(w.H, chunk, *b, out=y_out)[0] for b in bufs]
         for i in range(warmup):
-            fa.attention_forward(w.H, chunk, *bufs[i % nbuf])
+            calls[i % nbuf]()
         barrier()
         sampler = ClockSampler(local_rank) if sample_clocks else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -398,7 +406,7 @@ def run_ours(args, workload, rank: int, world: int, local_rank: int) -> dict | N
             sampler.start()
         e0.record()
         for i in range(steps):
-            fa.attention_forward(w.H, chunk, *bufs[i % nbuf])
+            calls[i % nbuf]()
         e1.record()
         while not e1.query():
             time.sleep(0.0002)

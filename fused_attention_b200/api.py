@@ -72,6 +72,37 @@ def attention_forward(head_dim: int, chunk_size: int, queries: torch.Tensor, key
     return out
 
 
+def bind_forward(head_dim: int, chunk_size: int, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
+                 mask: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None,
+                 flags: int = _lib.FLAG_DEFAULT):
+    """The same call with its arguments checked and converted once: returns ``(launch, out)`` where ``launch()``
+    does nothing but call ``fa_b200_attention_forward`` on the current stream of the tensors' device, writing
+    into ``out``.  For loops over fixed tensors (benchmarks, CUDA-graph capture), where the checks and the
+    allocation of ``attention_forward`` would cost more than a small problem's kernel."""
+    lib = _lib.load()
+    probe = attention_forward   # the checks live there; run them once on these tensors
+    y = probe(head_dim, chunk_size, queries, keys, values, mask, flags=flags)
+    if out is None:
+        out = y
+    else:
+        _check_tensor(out, "out")
+        _require(tuple(out.shape) == tuple(queries.shape) and out.device == queries.device, "out must match queries")
+    B, L, F = queries.shape
+    dev = queries.device.index if queries.device.index is not None else torch.cuda.current_device()
+    ptrs = (queries.data_ptr(), keys.data_ptr(), values.data_ptr(), mask.data_ptr() if mask is not None else None,
+            out.data_ptr())
+    fn, device, H, C, fl = lib.fa_b200_attention_forward, queries.device, int(head_dim), int(chunk_size), int(flags)
+    keep = (queries, keys, values, mask, out)   # the tensors live as long as the closure
+
+    def launch() -> None:
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = fn(ptrs[0], ptrs[1], ptrs[2], ptrs[3], ptrs[4], B, L, F, H, C, dev, ctypes.c_void_p(stream), fl)
+        if rc != 0:
+            _lib.check(rc)
+    launch.tensors = keep
+    return launch, out
+
+
 def attention_forward_host(head_dim: int, chunk_size: int, queries: torch.Tensor, keys: torch.Tensor,
                            values: torch.Tensor, mask: Optional[torch.Tensor] = None, *, device: int = 0,
                            out: Optional[torch.Tensor] = None, flags: int = _lib.FLAG_DEFAULT) -> torch.Tensor:

@@ -833,3 +833,19 @@ def test_torch_free_driver_program(shape):
     r = subprocess.run([exe, *map(str, shape), "5"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "differ in 0 values" in r.stdout
+
+
+def test_bound_call_is_the_same_launch():
+    """bind_forward checks and converts the arguments once; its launch() writes the same bits into `out` as
+    attention_forward returns, call after call, and rejects what attention_forward rejects."""
+    q, k, v = (t.cuda() for t in make_inputs(2, 700, 3 * 128, 1.0, 77))
+    out = torch.zeros_like(q)
+    launch, y = fa.bind_forward(128, 64, q, k, v, out=out)
+    assert y is out
+    for _ in range(3):
+        out.zero_()
+        launch()
+        torch.cuda.synchronize()
+        assert torch.equal(out, fa.attention_forward(128, 64, q, k, v))
+    with pytest.raises(Exception):
+        fa.bind_forward(128, 64, q, k[:, :10], v)
