@@ -356,11 +356,16 @@ const SplitScratch* scratch_for_stream(DeviceCtx& c, cudaStream_t st) {
 // round is divided stays on single CTAs), and a number of 256-row blocks per (batch, head) that is even or
 // large, since a pair works on 512 rows and an odd block leaves one CTA of a pair without work.  Measured on
 // the headline shape: the same SM clocks per launch as on single CTAs, but less shared-memory and L2 traffic,
-// so under the power cap the SMs clock 2 to 3 % higher.
-bool use_pair_kernel(uint32_t H, bool mask_ok, uint32_t q_pairs, uint32_t tail_steps, uint32_t flags) {
-    if (H != 128 || !mask_ok || (flags & FA_B200_FLAG_NO_PAIR)) return false;
+// so under the power cap the SMs clock 2 to 3 % higher.  Without a mask it is left alone when the pairs of SMs
+// get at most one work item each (`heads` = batch entries x heads): setting up and leaving in pairs then costs
+// more than it gains (measured 1 to 1.5 % slower with one item per pair, equal with two, 2 % faster from three on);
+// with a mask the pairs' mask buffer per query tile decides.
+bool use_pair_kernel(uint32_t H, bool has_mask, bool mask_ok, uint32_t q_pairs, uint32_t heads, uint32_t sms,
+                     uint32_t tail_steps, uint32_t flags) {
+    if (H != 128 || (has_mask && !mask_ok) || (flags & FA_B200_FLAG_NO_PAIR)) return false;
     if (flags & FA_B200_FLAG_FORCE_PAIR) return true;
     if (tail_steps != 0) return false;
+    if (!has_mask && static_cast<uint64_t>((q_pairs + 1u) / 2u) * heads <= sms / 2u) return false;
     return (q_pairs % 2u) == 0u || q_pairs >= 16u;
 }
 
@@ -494,7 +499,8 @@ int forward_device(const void* q, const void* k, const void* v, const void* mask
                     CUtensorMap mm = mq;
                     p.mask_tma = (mask && mask_rows_aligned(mask, L)) ? 1u : 0u;
                     if (rc == FA_B200_OK && p.mask_tma) rc = make_mask_map(&mm, mask, B, L);
-                    if (rc == FA_B200_OK && use_pair_kernel(H, !mask || p.mask_tma, p.q_pairs, sch.tail_steps, flags)) {
+                    if (rc == FA_B200_OK && use_pair_kernel(H, mask != nullptr, p.mask_tma != 0u, p.q_pairs, p.R * B,
+                                                            static_cast<uint32_t>(c->sm_count), sch.tail_steps, flags)) {
                         // K as halves of a tile: boxes of 64 keys x 64 columns
                         CUtensorMap mkh;
                         rc = make_map(&mkh, k, B, L, F, H, 64);
@@ -987,7 +993,7 @@ int fa_b200_describe_schedule(uint32_t B, uint32_t L, uint32_t F, uint32_t head_
     const Schedule s = make_schedule(n_items, n, sm_count,
                                      (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
     const uint32_t q_pairs = (L + 2 * fa::kTile - 1) / (2 * fa::kTile);
-    if (use_pair_kernel(head_dim, true, q_pairs, s.tail_steps, flags) && sm_count >= 2) {
+    if (use_pair_kernel(head_dim, false, true, q_pairs, (F / head_dim) * B, sm_count, s.tail_steps, flags) && sm_count >= 2) {
         // pairs of CTAs: work items of 512 query rows, one cluster of two CTAs per pair of SMs
         const uint32_t quads = ((q_pairs + 1) / 2) * (F / head_dim) * B, clusters = quads < sm_count / 2 ? quads : sm_count / 2;
         out[0] = 3;
@@ -1022,7 +1028,8 @@ int fa_b200_select_kernel(uint32_t B, uint32_t L, uint32_t F, uint32_t head_dim,
     const Schedule s = make_schedule(q_pairs * (F / head_dim) * B, n, static_cast<uint32_t>(sms),
                                      (flags & (FA_B200_FLAG_NO_SPLIT | FA_B200_FLAG_FORCE_PAIR)) == 0);
     // (a mask is taken to start on a 16-byte boundary here)
-    return use_pair_kernel(head_dim, !has_mask || (L & 7u) == 0u, q_pairs, s.tail_steps, flags) ? 3 : 2;
+    return use_pair_kernel(head_dim, has_mask != 0, (L & 7u) == 0u, q_pairs, (F / head_dim) * B,
+                           static_cast<uint32_t>(sms), s.tail_steps, flags) ? 3 : 2;
 }
 
 }  // extern "C"

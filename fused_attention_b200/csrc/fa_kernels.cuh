@@ -309,6 +309,28 @@ __device__ __forceinline__ void store_o_row(uint32_t tO, float inv_l, __half* ds
     }
 }
 
+// One O row from TMEM, multiplied by `inv_l` and converted to fp16, into a staging area in shared memory from
+// where TMA stores it: for a thread with registers to spare (a softmax thread), the whole row in one round trip.
+// The area holds, per 64 columns, one box of the Y map (32 rows of 128 bytes with the 128-byte swizzle: 16-byte
+// piece c of row r at piece c ^ (r & 7)); `stage` is 1024-byte aligned, `lane` the row within the box.
+template <int H>
+__device__ __forceinline__ void stage_o_row(uint32_t tO, float inv_l, uint32_t stage, uint32_t lane) {
+    static_assert(H % 64 == 0, "boxes of 64 columns");
+    float o[H];
+#pragma unroll
+    for (int c0 = 0; c0 < H; c0 += 32) tmem_ld32(tO + c0, o + c0);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < H; i += 8) {
+        const uint32_t w0 = pack_half2(o[i] * inv_l, o[i + 1] * inv_l);
+        const uint32_t w1 = pack_half2(o[i + 2] * inv_l, o[i + 3] * inv_l);
+        const uint32_t w2 = pack_half2(o[i + 4] * inv_l, o[i + 5] * inv_l);
+        const uint32_t w3 = pack_half2(o[i + 6] * inv_l, o[i + 7] * inv_l);
+        const uint32_t piece = static_cast<uint32_t>((i % 64) / 8) ^ (lane & 7u);
+        st_shared_v4(stage + static_cast<uint32_t>(i / 64) * 4096u + lane * 128u + piece * 16u, w0, w1, w2, w3);
+    }
+}
+
 // Scores of one row (TMEM -> registers).
 __device__ __forceinline__ void load_s_row(uint32_t tS, float (&s)[kTile]) {
     tmem_ld32(tS, s);
@@ -601,6 +623,11 @@ struct PipeCfg {
     // the P buffer to be free of the previous step's P V.  Measured at H = 128: 1 (-2.4 %; 2 and 3
     // spill); at H = 64 holding any back costs more than it hides.
     static constexpr int kHeldChunks = H == 128 ? 1 : 0;
+    // Whether the softmax warps write Y of the CTA's last segment themselves when it is a whole work item (both
+    // tiles at once, nothing being left to overlap an epilogue with) instead of handing it to the epilogue warps.
+    // Measured: H = 128 1 to 2 % fewer SM clocks on launches of one or two items per CTA, nothing on long ones;
+    // H = 64 2 % more on every shape (the extra code costs the row pass registers).
+    static constexpr bool kSoftmaxWritesLast = H == 128;
 };
 
 // Into how many parts the key axis of one work item may be divided (see Plan).
@@ -1200,22 +1227,27 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // barrier may run at most one phase ahead of the epilogue's wait, so the previous segment's
             // O must have been read out first (always true already when a segment has two or more
             // key steps).
-            if (k > 0) mbar_wait(bar(BAR_OFREE0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OFREE0 + i));
-            l_buf[k & 1u][i][row] = l;
-            m_buf[k & 1u][i][row] = m;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
+            // (With kSoftmaxWritesLast the CTA's last segment is finished by these warps themselves, below.)
+            if (!C::kSoftmaxWritesLast || k + 1u < nseg) {
+                if (k > 0) mbar_wait(bar(BAR_OFREE0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OFREE0 + i));
+                l_buf[k & 1u][i][row] = l;
+                m_buf[k & 1u][i][row] = m;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
+            }
         }
-        // ---- parts of divided items ---------------------------------------------------------------
+        // ---- the CTA's last segment ---------------------------------------------------------------
         // If this CTA's last segment is a part of a divided item, these warps finish it themselves:
         // they have nothing else left to do, they have the registers to keep many loads in flight, and
         // the part's rows can come straight from TMEM.  A warp that finds every other part of its 32
         // rows already counted in adds the parts up and writes Y; otherwise it leaves its rows in the
         // CTA's scratch slot and counts itself in (and adds up after all if that made it the last).
         const uint32_t wq = warp & 3u;
+        bool last_is_whole = C::kSoftmaxWritesLast && nseg > 0u;
         if (ntail > 0u) {   // the CTA's last segment is a tail segment
             const Seg sg = get_seg(pl_s, t0, p, nseg - 1u);
             if (sg.partial) {
+                last_is_whole = false;
                 const uint32_t tail_item = seg_tail_item(pl_s, t0, nseg - 1u);
                 const PartsOf po = parts_of(p, tail_item);
                 const uint32_t mine = blockIdx.x - po.c_first;
@@ -1257,6 +1289,30 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
         }
+        if constexpr (C::kSoftmaxWritesLast) if (last_is_whole) {
+            // A whole work item: nothing is left to overlap its epilogue with, so these warps write Y themselves,
+            // both tiles at once (each thread has its row sum, and the registers to take the whole O row in one
+            // round trip), instead of handing the two tiles to the four epilogue warps one after the other.
+            // Staging area: the tile's own query buffer, which its last Q K^T has long let go of.
+            const Seg sg = get_seg(pl_s, t0, p, nseg - 1u);
+            const uint32_t bh = sg.item / q_pairs;
+            const int32_t row0 = static_cast<int32_t>(((sg.item % q_pairs) * 2u + i) * kTile + wq * 32u);
+            const uint32_t stage = q_addr(nseg - 1u, i) + wq * static_cast<uint32_t>((H / 64) * 4096);
+            mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+            tc_fence_after();
+            __syncwarp();
+            stage_o_row<H>(tO, 1.f / l, stage, lane);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < static_cast<int32_t>(p.L)) {
+#pragma unroll
+                for (int half = 0; half < H / 64; ++half)
+                    tma_store_3d(&tmY, stage + half * 4096u, static_cast<int32_t>((bh % p.R) * H + half * 64), row0,
+                                 static_cast<int32_t>(bh / p.R));
+                bulk_commit_group();
+            }
+            if (lane == 0) bulk_wait_read_all();   // the staging area is this CTA's until TMA has read it
+        }
         // A part that the epilogue warps put into scratch (the first tail segment of a CTA that has two) and
         // that turned out to be the last of its item: added up here, every part read from scratch.
         if (ntail == 2u) {
@@ -1291,7 +1347,8 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t g_end = 0;   // global steps up to and including the current segment
         for (uint32_t k = 0; k < nseg; ++k) {
             const Seg sg = get_seg(pl_s, t0, p, k);
-            if (sg.partial && k + 1u == nseg) break;   // the softmax warps finish a final part themselves
+            // the softmax warps finish a final part themselves, and with kSoftmaxWritesLast a final whole item too
+            if (k + 1u == nseg && (sg.partial || C::kSoftmaxWritesLast)) break;
             g_end += sg.len;
             const uint32_t q_pair = sg.item % q_pairs, bh = sg.item / q_pairs;
             const uint32_t head = bh % p.R, batch = bh / p.R;

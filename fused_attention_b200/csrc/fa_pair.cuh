@@ -190,6 +190,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const uint32_t tO = tmem_base + lane_off + (i ? C::kColO1 : C::kColO0);
         const float c = p.scale_log2;
         uint32_t g = 0;   // global step
+        float l_last = 1.f;
         for (uint32_t k = 0; k < my_items; ++k) {
             float m = -INFINITY, l = 0.f;
             for (uint32_t j = 0; j < n; ++j, ++g) {
@@ -251,10 +252,38 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(lbar(BAR_P0 + i));
             }
-            if (k > 0) mbar_wait(bar(BAR_OLOCAL0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OLOCAL0 + i));
-            l_buf[k & 1u][i][row] = l;
+            l_last = l;
+            if (k + 1u < my_items) {   // (the CTA's last item: see below)
+                if (k > 0) mbar_wait(bar(BAR_OLOCAL0 + i), (k - 1u) & 1u, ctl, kRoleSoftmax | (BAR_OLOCAL0 + i));
+                l_buf[k & 1u][i][row] = l;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
+            }
+        }
+        if (my_items > 0u) {
+            // The CTA's last item: nothing is left to overlap its epilogue with, so the softmax warps write Y
+            // themselves, both tiles at once (each thread has its row sum, and the registers to take the whole O row
+            // in one round trip), instead of handing the two tiles to the four epilogue warps one after the other.
+            // Staging area: the tile's own query buffer, which its last Q K^T has long let go of; 8 KiB per warp.
+            const uint32_t item = cluster + (my_items - 1u) * n_clusters;
+            const uint32_t q_quad = item % q_quads, bh = item / q_quads;
+            const uint32_t wq = warp & 3u;
+            const int32_t row0 = static_cast<int32_t>(((q_quad * 2u + rank) * 2u + i) * kTile + wq * 32u);
+            const uint32_t stage = sQ + i * G::kTileBytes + wq * 8192u;
+            mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
+            tc_fence_after();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAR_A0 + i));
+            stage_o_row<H>(tO, 1.f / l_last, stage, lane);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < static_cast<int32_t>(p.L)) {
+#pragma unroll
+                for (int half = 0; half < H / 64; ++half)
+                    tma_store_3d(&tmY, stage + half * 4096u, static_cast<int32_t>((bh % p.R) * H + half * 64), row0,
+                                 static_cast<int32_t>(bh / p.R));
+                bulk_commit_group();
+            }
+            if (lane == 0) bulk_wait_read_all();   // the staging area is this CTA's until TMA has read it
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ epilogue: Y = O / l, this CTA's tiles
@@ -264,7 +293,8 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const uint32_t lane_off = (wq * 32u) << 16;
         const uint32_t stage = sStage + wq * 4096u;
         uint32_t k = 0;
-        for (uint32_t item = cluster; item < n_items; item += n_clusters, ++k) {
+        // (the CTA's last item is written by the softmax warps)
+        for (uint32_t item = cluster; k + 1u < my_items; item += n_clusters, ++k) {
             const uint32_t q_quad = item % q_quads, bh = item / q_quads;
             const uint32_t head = bh % p.R, batch = bh / p.R;
 #pragma unroll

@@ -59,8 +59,9 @@ enum {
                                           that runs on pairs
                                           of CTAs (one MMA of 256 rows for two SMs); implies whole work
                                           items.  By default it is taken for such calls when their last
-                                          round is not divided and the sequence has an even or large
-                                          number of 256-row blocks                                   */
+                                          round is not divided, the sequence has an even or large
+                                          number of 256-row blocks and (without a mask) the pairs of SMs
+                                          get more than one work item each                           */
     FA_B200_FLAG_NO_PAIR = 64u,        /* never use that kernel                                      */
     FA_B200_FLAG_NO_SPLIT = 16u        /* never divide the key axis of one (batch, head, query rows)
                                           problem among several CTAs.  By default the warp-specialised

@@ -111,6 +111,9 @@ def test_kernel_selection(lib):
     assert sel(4, 2048, 4096, 128, 0, 0) == 3      # headline: pipelined, on pairs of CTAs
     assert sel(4, 2048, 4096, 128, 0, _lib.FLAG_NO_PAIR) == 2
     assert sel(4, 2048, 4096, 128, 1, 0) == 3      # with a mask too, its rows being 16-byte aligned
+    assert sel(4, 2048, 512, 128, 0, 0) == 2       # 64 blocks of 512 rows for 74 pairs of SMs: single CTAs
+    assert sel(4, 2048, 512, 128, 1, 0) == 3       # ... but pairs with a mask (a mask buffer per query tile)
+    assert sel(4, 2048, 1024, 128, 0, 0) == 3      # 128 blocks: two rounds of pairs
     assert sel(4, 2044, 4096, 128, 1, 0) == 2      # mask rows that TMA cannot fetch: single CTAs
     assert sel(1, 16384, 4096, 128, 0, 0) == 3
     assert sel(1, 16384, 512, 128, 0, 0) == 2      # the last round of this one is divided: single CTAs
