@@ -6,7 +6,8 @@
   bin/fa_b200_driver  torch-free C++ program over the C ABI (fill, run, check, time)
 
 Run ``python -m fused_attention_b200.build [--ext] [--driver] [--debug] [--cycles]`` (``--debug`` also builds the
-checked library ``lib/libfa_b200_debug.so``, ``--cycles`` the clock-counting one ``lib/libfa_b200_cycles.so``).
+checked library ``lib/libfa_b200_debug.so``, ``--cycles`` the clock-counting ones ``lib/libfa_b200_cycles.so`` and
+``lib/libfa_b200_timeline.so``).
 Nothing is installed outside the tree.
 """
 from __future__ import annotations
@@ -25,6 +26,7 @@ EXTDIR = os.path.join(HERE, "ext")
 LIB = os.path.join(LIBDIR, "libfa_b200.so")
 DEBUG_LIB = os.path.join(LIBDIR, "libfa_b200_debug.so")   # the checked build (-DFA_DEBUG), used by one GPU test
 CYCLES_LIB = os.path.join(LIBDIR, "libfa_b200_cycles.so")  # the clock-counting build (-DFA_CYCLES), see cycles.py
+TIMELINE_LIB = os.path.join(LIBDIR, "libfa_b200_timeline.so")  # ... with per-step time stamps (-DFA_TIMELINE) as well
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -51,20 +53,25 @@ def lib_sources() -> list[str]:
         os.path.join(ROOT, "include", "fa_b200.h")]
 
 
-def build_lib(force: bool = False, verbose: bool = False, debug: bool = False, cycles: bool = False) -> str:
+def build_lib(force: bool = False, verbose: bool = False, debug: bool = False, cycles: bool = False,
+              timeline: bool = False) -> str:
     """Compile csrc/fa_b200.cu into lib/libfa_b200.so (cross-compiles without a GPU).
 
     ``debug`` builds lib/libfa_b200_debug.so instead, with -DFA_DEBUG: every TMA copy and tensor-memory
     access checks its operands first (see the checked-build section of csrc/fa_ptx.cuh).
     ``cycles`` builds lib/libfa_b200_cycles.so, with -DFA_CYCLES: CTA 0 of the warp-specialised kernels
-    records time stamps and its SM clock count per launch (read by cycles.py)."""
+    records time stamps and its SM clock count per launch (read by cycles.py).
+    ``timeline`` builds lib/libfa_b200_timeline.so, with -DFA_CYCLES -DFA_TIMELINE: one warp per role of CTA 0 of
+    the kernel on pairs of CTAs also stamps the events of every key step (cycles.py --timeline)."""
     os.makedirs(LIBDIR, exist_ok=True)
-    out = DEBUG_LIB if debug else (CYCLES_LIB if cycles else LIB)
+    out = DEBUG_LIB if debug else (TIMELINE_LIB if timeline else (CYCLES_LIB if cycles else LIB))
     if not force and not _stale(out, lib_sources()):
         return out
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if debug:
         cmd += ["-DFA_DEBUG"]
+    elif timeline:
+        cmd += ["-DFA_CYCLES", "-DFA_TIMELINE"]
     elif cycles:
         cmd += ["-DFA_CYCLES"]
     if verbose:
@@ -131,6 +138,7 @@ def main(argv: list[str]) -> int:
         print(build_lib(force=force, verbose="-v" in argv, debug=True))
     if "--cycles" in argv:
         print(build_lib(force=force, verbose="-v" in argv, cycles=True))
+        print(build_lib(force=force, verbose="-v" in argv, timeline=True))
     if "--ext" in argv:
         print(build_ext(force=force))
     if "--driver" in argv:

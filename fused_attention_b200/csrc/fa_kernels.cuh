@@ -588,6 +588,21 @@ fa_fwd_simple(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
 }
 
+// Time line of the key-step loop, only in builds with -DFA_CYCLES -DFA_TIMELINE (the pair kernel has the stamps):
+// lane 0 of one warp per role of CTA 0 writes its SM clock at event `ev` of global key step `g` into word
+// 256 + ((role * 256 + g) * 8 + ev) of the buffer given to fa_b200_debug_cycles (9 * 1024 words in such a build);
+// steps beyond 255 are not recorded.  Roles: 0, 1 a softmax warp of query tile 0, 1; 2 the warp issuing Q K^T;
+// 3 the warp issuing P V.  Events are listed where the stamps are.
+#if defined(FA_CYCLES) && defined(FA_TIMELINE)
+#define FA_STAMP(role, g, ev)                                                                         \
+    do {                                                                                              \
+        if (p.cycles != nullptr && blockIdx.x == 0 && lane == 0 && (g) < 256u)                        \
+            p.cycles[256u + (((role) * 256u + (g)) * 8u) + (ev)] = static_cast<unsigned long long>(clock64()); \
+    } while (0)
+#else
+#define FA_STAMP(role, g, ev) do { } while (0)
+#endif
+
 // ============================================================================ pipelined kernel
 template <int H, bool kHasMask = false>
 struct PipeCfg {

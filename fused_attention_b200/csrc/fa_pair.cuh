@@ -194,13 +194,18 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         for (uint32_t k = 0; k < my_items; ++k) {
             float m = -INFINITY, l = 0.f;
             for (uint32_t j = 0; j < n; ++j, ++g) {
+                // (time line, softmax warp of rows 0-31: 0 looks for S, 1 S there, 2 S in registers, 3 first 32
+                // exponentials taken, 4 P buffer free, 5 all exponentials taken and P stored, 6 P handed over)
+                if ((warp & 3u) == 0u) FA_STAMP(i, g, 0);
                 mbar_wait(bar(BAR_S0 + i), g & 1u, ctl, kRoleSoftmax | (BAR_S0 + i));
+                if ((warp & 3u) == 0u) FA_STAMP(i, g, 1);
                 tc_fence_after();
                 __syncwarp();
                 float s[kTile];
                 const bool ragged = (j + 1) * kTile > p.L;
                 const bool first = j == 0;
                 load_s_row(tS, s);
+                if ((warp & 3u) == 0u) FA_STAMP(i, g, 2);
                 // S is in registers: the leader may overwrite it (in both CTAs) with the next scores
                 tc_fence_before();
                 __syncwarp();
@@ -222,13 +227,16 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     uint32_t held[16 * C::kHeldChunks];
                     float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, nmc, tP, mx4, held);
+                    if ((warp & 3u) == 0u) FA_STAMP(i, g, 3);
                     if (g > 0) {
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
                         tc_fence_after();
                     }
+                    if ((warp & 3u) == 0u) FA_STAMP(i, g, 4);
 #pragma unroll
                     for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
                     sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, nmc, tP, mx4);
+                    if ((warp & 3u) == 0u) FA_STAMP(i, g, 5);
                     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                     const bool moved = (mx - m) * c > kLazyRescaleLog2;
                     if (__any_sync(0xffffffffu, moved)) {
@@ -251,6 +259,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(lbar(BAR_P0 + i));
+                if ((warp & 3u) == 0u) FA_STAMP(i, g, 6);
             }
             l_last = l;
             if (k + 1u < my_items) {   // (the CTA's last item: see below)
@@ -374,17 +383,24 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     const bool new_item = j == 0;
                     const bool last_of_item = j + 1 == n;
                     const uint32_t tk = 2 * g;
+                    // (time line: 0 top of the step, 1 K and Q there, 2 S buffer read by tile 1: tile 0's Q K^T goes
+                    // out, 3 issued, 4 S buffer read by tile 0: tile 1's Q K^T goes out, 5 issued)
+                    FA_STAMP(2u, g, 0);
                     if (!(polled && mbar_poll_end<0>())) wait_full(tk);
                     if (new_item) mwait(BAR_QFULL0, k & 1u);
+                    FA_STAMP(2u, g, 1);
                     if (g > 0) mwait(BAR_SFREE, 1u);
+                    FA_STAMP(2u, g, 2);
                     tc_fence_after();
                     if (leader && ok) {
                         issue_qk_pair(tS, sQ, slot_addr(tk));
                         commit_both(BAR_S0);
                         if (last_of_item) commit_both(BAR_QEMPTY0);
                     }
+                    FA_STAMP(2u, g, 3);
                     if (new_item) mwait(BAR_QFULL1, k & 1u);
                     mwait(BAR_SFREE, 0u);
+                    FA_STAMP(2u, g, 4);
                     tc_fence_after();
                     polled = g + 1 < steps;
                     if (polled) {
@@ -397,6 +413,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                         if (last_of_item) commit_both(BAR_QEMPTY1);
                         commit_both(BAR_EMPTY + (tk % NS));
                     }
+                    FA_STAMP(2u, g, 5);
                     if (++j == n) { j = 0; ++k; }
                 }
             } else {
@@ -406,16 +423,23 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 for (uint32_t g = 0; g < steps; ++g) {
                     const uint32_t tv = 2 * g + 1;
                     const uint32_t acc = j > 0 ? 1u : 0u;
+                    // (time line: 0 top of the step, 1 V there and O free, 2 P of tile 0 there: its P V goes out,
+                    // 3 issued, 4 P of tile 1 there: its P V goes out, 5 issued)
+                    FA_STAMP(3u, g, 0);
                     if (!(polled && mbar_poll_end<1>())) wait_full(tv);
                     if (j == 0 && k > 0) mwait(BAR_OFREE0, (k - 1u) & 1u);
+                    FA_STAMP(3u, g, 1);
                     mwait(BAR_P0, g & 1u);
+                    FA_STAMP(3u, g, 2);
                     tc_fence_after();
                     if (leader && ok) {
                         issue_pv_pair(tO0, tP0, slot_addr(tv), acc);
                         commit_both(BAR_PV0);
                     }
+                    FA_STAMP(3u, g, 3);
                     if (j == 0 && k > 0) mwait(BAR_OFREE1, (k - 1u) & 1u);
                     mwait(BAR_P1, g & 1u);
+                    FA_STAMP(3u, g, 4);
                     tc_fence_after();
                     polled = g + 1 < steps;
                     if (polled) {
@@ -427,6 +451,7 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                         commit_both(BAR_PV1);
                         commit_both(BAR_EMPTY + (tv % NS));
                     }
+                    FA_STAMP(3u, g, 5);
                     if (++j == n) { j = 0; ++k; }
                 }
             }

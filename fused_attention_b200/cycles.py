@@ -9,6 +9,14 @@ it the figure to compare two versions of a kernel by.
     python -m fused_attention_b200.cycles B R L H [flags]      # e.g. 4 32 2048 128 32
 
 prints the medians over a loop of launches; ``measure`` returns them.
+
+The time-line build (-DFA_CYCLES -DFA_TIMELINE, same build command) also stamps, for the kernel on pairs of
+CTAs at head_dim 128, the events of every key step as seen by one softmax warp of each query tile and by the two
+warps that issue the MMAs:
+
+    python -m fused_attention_b200.cycles --timeline B R L H   # e.g. --timeline 4 32 2048 128
+
+prints where a key step's clocks go (``timeline`` returns the same as a dict).
 """
 from __future__ import annotations
 
@@ -19,10 +27,11 @@ import sys
 from . import build
 
 
-def _load() -> ctypes.CDLL:
-    if not os.path.exists(build.CYCLES_LIB):
-        raise RuntimeError(f"{build.CYCLES_LIB} is missing: python -m fused_attention_b200.build --cycles")
-    lib = ctypes.CDLL(build.CYCLES_LIB)
+def _load(path: str | None = None) -> ctypes.CDLL:
+    path = path or build.CYCLES_LIB
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: python -m fused_attention_b200.build --cycles")
+    lib = ctypes.CDLL(path)
     u32, vp, i32 = ctypes.c_uint32, ctypes.c_void_p, ctypes.c_int
     lib.fa_b200_attention_forward.restype = i32
     lib.fa_b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, i32, vp, u32]
@@ -95,8 +104,89 @@ def measure(B: int, R: int, L: int, H: int, flags: int = 0, launches: int = 40, 
     return out
 
 
+TIMELINE_WORDS = 9 * 1024      # 256 words of launch records, then 4 roles x 256 key steps x 8 events
+_SOFTMAX_EVENTS = ("looks for S", "S there", "S in registers", "first 32 exponentials taken", "P buffer free",
+                   "exponentials taken, P stored", "P handed over")
+
+
+def parse_timeline(words: list[int], lo: int = 20, hi: int = 100) -> dict:
+    """Mean durations (SM clocks) over key steps [lo, hi) of CTA 0 from the words the time-line build wrote behind
+    the launch records: role 0, 1 = a softmax warp of query tile 0, 1 (events as in _SOFTMAX_EVENTS), role 2 = the
+    warp issuing Q K^T (0 top of the step, 1 K there, 2 issues tile 0's, 3 issued, 4 issues tile 1's, 5 issued),
+    role 3 = the warp issuing P V (the same with V and P).  A stamp of 0 means "not reached"."""
+    def at(role, g, ev):
+        return words[256 + (role * 256 + g) * 8 + ev]
+
+    def mean(xs):
+        xs = [x for x in xs if x is not None]
+        return sum(xs) / len(xs) if xs else None
+
+    def span(role_a, ev_a, role_b, ev_b, dg=0):
+        out = []
+        for g in range(lo, hi - dg):
+            a, b = at(role_a, g, ev_a), at(role_b, g + dg, ev_b)
+            if a and b:
+                out.append(b - a)
+        return mean(out)
+
+    res = {"steps_recorded": sum(1 for g in range(256) if at(2, g, 2)),
+           "step_period": span(2, 2, 2, 2, 1)}
+    for i in (0, 1):
+        res[f"tile{i}"] = {
+            "wait_for_S": span(i, 0, i, 1), "S_into_registers_and_first_32_exponentials": span(i, 1, i, 3),
+            "wait_for_P_buffer": span(i, 3, i, 4), "other_96_exponentials_and_P_stores": span(i, 4, i, 5),
+            "hand_over": span(i, 5, i, 6), "pass": span(i, 1, i, 6),
+        }
+    res["qk_warp"] = {"wait_for_K": span(2, 0, 2, 1), "wait_for_S_read_by_tile1": span(2, 1, 2, 2),
+                      "wait_for_S_read_by_tile0": span(2, 3, 2, 4)}
+    res["pv_warp"] = {"wait_for_V": span(3, 0, 3, 1), "wait_for_P0": span(3, 1, 3, 2), "wait_for_P1": span(3, 3, 3, 4)}
+    res["S_finished_before_its_tile_looks"] = {
+        # Q K^T of tile i issued -> its softmax warp sees S: MMA time + hand-over + how long the warp was still busy
+        "tile0_issue_to_seen": span(2, 2, 0, 1), "tile1_issue_to_seen": span(2, 4, 1, 1)}
+    return res
+
+
+def timeline(B: int, R: int, L: int, H: int = 128, device: int = 0) -> dict:
+    """One launch of the kernel on pairs of CTAs (forced) after a few warm-up launches; its time line parsed."""
+    import torch
+    from .workloads import make_inputs
+    from ._lib import FLAG_FORCE_PAIR
+
+    lib = _load(build.TIMELINE_LIB)
+    dev = torch.device("cuda", device)
+    torch.cuda.set_device(device)
+    buf = torch.zeros(TIMELINE_WORDS, dtype=torch.int64, device=dev)
+    lib.fa_b200_debug_cycles(buf.data_ptr())
+    ins = [tuple(t.to(dev) for t in make_inputs(B, L, R * H, 0.5, 100 + i)) for i in range(3)]
+    y = torch.empty_like(ins[0][0])
+    try:
+        for i in range(7):
+            if i == 6:
+                torch.cuda.synchronize(dev)
+                buf.zero_()
+            q, k, v = ins[i % 3]
+            rc = lib.fa_b200_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, y.data_ptr(), B, L, R * H,
+                                               H, 0, device, None, FLAG_FORCE_PAIR)
+            if rc != 0:
+                raise RuntimeError(f"fa_b200_attention_forward returned {rc}")
+        torch.cuda.synchronize(dev)
+        words = buf.cpu().tolist()
+    finally:
+        lib.fa_b200_debug_cycles(None)
+    steps = sum(1 for g in range(256) if words[256 + (2 * 256 + g) * 8 + 2])
+    return parse_timeline(words, lo=min(20, steps // 4), hi=max(min(100, steps - 4), min(20, steps // 4) + 1))
+
+
 if __name__ == "__main__":
-    a = [int(x) for x in sys.argv[1:]]
+    args = sys.argv[1:]
+    if args and args[0] == "--timeline":
+        a = [int(x) for x in args[1:]]
+        if len(a) not in (3, 4):
+            sys.exit(__doc__)
+        import json
+        print(json.dumps(timeline(*a), indent=1))
+        sys.exit(0)
+    a = [int(x) for x in args]
     if len(a) not in (4, 5):
         sys.exit(__doc__)
     print(measure(*a))

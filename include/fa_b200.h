@@ -199,7 +199,11 @@ int fa_b200_selftest_debug_checks(int device, uint32_t out[4]);
  * warp-specialised kernels writes, per launch, four 64-bit words into record (launch id mod 64) of the
  * given device buffer of 256 words: the global timer (ns) at its entry, after its wait for the previous
  * kernel of the stream and at its end, and its SM clock count between the last two.  NULL stops the
- * recording.  The buffer must outlive the launches.  No counterpart in the reference.
+ * recording.  The buffer must outlive the launches.  A build with -DFA_TIMELINE as well needs a buffer of
+ * 9 * 1024 words: behind the 256, lane 0 of one warp per role of CTA 0 of the kernel on pairs of CTAs writes
+ * its SM clock at up to eight events of each of the first 256 key steps (word 256 + (role * 256 + step) * 8 +
+ * event; the roles and events are listed in csrc/fa_kernels.cuh and csrc/fa_pair.cuh).  No counterpart in the
+ * reference.
  */
 int fa_b200_debug_cycles(void* device_buffer_of_256_u64);
 #endif

@@ -32,9 +32,11 @@ def test_library_exports_every_declared_symbol(lib, repo_root):
     from fused_attention_b200 import build
     if os.path.exists(build.CYCLES_LIB):
         import ctypes
-        variant_lib = ctypes.CDLL(build.CYCLES_LIB)
-        for name in declared | only_variant:
-            assert getattr(variant_lib, name) is not None
+        for path in (build.CYCLES_LIB, build.TIMELINE_LIB):
+            if os.path.exists(path):
+                variant_lib = ctypes.CDLL(path)
+                for name in declared | only_variant:
+                    assert getattr(variant_lib, name) is not None
 
 
 def test_python_constants_match_header(repo_root):

@@ -164,3 +164,30 @@ def test_clock_count_records_are_parsed_and_summarised():
     assert s["launches"] == 4 and s["sm_clocks"] == 300_002
     assert s["busy_us"] == 160.0 and s["period_us"] == 200.0 and s["gap_us"] == 40.0
     assert cycles.summarise([])["sm_clocks"] is None
+
+
+def test_time_line_words_are_parsed():
+    """cycles.parse_timeline on a synthetic buffer: key steps 2800 clocks apart, tile 1 lagging tile 0 by 1100,
+    a softmax pass of 2560 clocks per tile; stamps of steps that were not reached stay zero and are skipped."""
+    from fused_attention_b200 import cycles
+    w = [0] * cycles.TIMELINE_WORDS
+
+    def put(role, g, ev, v):
+        w[256 + (role * 256 + g) * 8 + ev] = v
+    for g in range(60):
+        t = 10_000 + g * 2800
+        for i in (0, 1):
+            for ev, off in enumerate((0, 120, 150, 950, 1120, 2520, 2680)):
+                put(i, g, ev, t + i * 1100 + off)
+        for ev, off in enumerate((0, 200, 900, 1100, 2300, 2500)):
+            put(2, g, ev, t + off - 600)
+        for ev, off in enumerate((0, 200, 1200, 1400, 2300, 2500)):
+            put(3, g, ev, t + off + 1500)
+    r = cycles.parse_timeline(w, 20, 100)      # steps 60..99 were never reached
+    assert r["steps_recorded"] == 60 and r["step_period"] == 2800.0
+    assert r["tile0"]["pass"] == 2560.0 and r["tile1"]["wait_for_S"] == 120.0
+    assert r["tile0"]["wait_for_P_buffer"] == 170.0 and r["tile0"]["hand_over"] == 160.0
+    assert r["qk_warp"] == {"wait_for_K": 200.0, "wait_for_S_read_by_tile1": 700.0, "wait_for_S_read_by_tile0": 1200.0}
+    assert r["pv_warp"]["wait_for_P0"] == 1000.0
+    assert r["S_finished_before_its_tile_looks"]["tile0_issue_to_seen"] == 10_000 + 120 - (10_000 + 900 - 600)
+    assert cycles.parse_timeline([0] * cycles.TIMELINE_WORDS)["step_period"] is None

@@ -705,6 +705,21 @@ def test_clock_counting_build_reports_a_launch(flags):
     assert 900.0 <= mhz <= 2100.0, (mhz, s)
 
 
+def test_time_line_build_reports_the_key_step():
+    """The -DFA_CYCLES -DFA_TIMELINE build: the stamps of one launch of the kernel on pairs of CTAs give a key step
+    of a few thousand SM clocks, a softmax pass that fits into it, and waits that are shorter than the step."""
+    from fused_attention_b200 import build, cycles
+    if not os.path.exists(build.TIMELINE_LIB):
+        pytest.skip("time-line library not built (python -m fused_attention_b200.build --cycles)")
+    r = cycles.timeline(2, 16, 4096, 128)      # 32 key steps per item, several items per pair of CTAs
+    assert r["steps_recorded"] >= 64, r
+    assert 1800.0 <= r["step_period"] <= 5000.0, r
+    for tile in ("tile0", "tile1"):
+        assert 1000.0 <= r[tile]["pass"] <= r["step_period"] * 1.05, r
+        assert 0.0 <= r[tile]["wait_for_S"] <= r["step_period"], r
+    assert r["qk_warp"]["wait_for_S_read_by_tile0"] <= r["step_period"], r
+
+
 # ---------------------------------------------------------------- drop-in module `fused_attn`
 def _fused_attn_module():
     ext_dir = os.path.join(os.path.dirname(fa.__file__), "ext")
