@@ -190,6 +190,41 @@ def test_many_random_shapes_against_fp32_attention_on_the_device(seed):
     assert not failures, failures
 
 
+def test_many_random_shapes_with_a_mask_against_fp32_attention_on_the_device():
+    """80 shapes with an additive mask (causal, or a padded tail, plus soft values) at head_dim 64 and 128 through
+    whatever kernel the launcher picks: lengths that are multiples of 8 (mask tiles through TMA, on pairs of CTAs
+    or on single ones) and lengths that are not (rows read from global memory); checker and tolerance as above."""
+    import random
+    rng = random.Random(7)
+    failures = []
+    for it in range(80):
+        H = rng.choice([64, 128])
+        B = rng.randint(1, 4)
+        R = rng.randint(1, 24)
+        L = rng.choice([rng.randint(1, 300), rng.randint(300, 1500), rng.randint(1500, 3000)])
+        if rng.random() < 0.6:
+            L = max(8, L // 8 * 8)
+        if B * R * L * L > 1.5e9:
+            R = max(1, int(1.5e9 / (B * L * L)))
+        g = torch.Generator(device="cuda")
+        g.manual_seed(5000 + it)
+        q, k, v = (torch.randn(B, L, R * H, generator=g, device="cuda").half() for _ in range(3))
+        mask = (0.5 * torch.randn(B, L, L, generator=g, device="cuda")).half()
+        if rng.random() < 0.5:
+            mask += torch.triu(torch.full((L, L), float("-inf"), device="cuda", dtype=torch.float16), diagonal=1)
+        else:
+            mask[:, :, L - L // 3:] = float("-inf") if L >= 3 else 0.0
+        y = fa.attention_forward(H, 32, q, k, v, mask)
+        y2 = fa.attention_forward(H, 32, q, k, v, mask)
+        qf, kf, vf = (t.float().view(B, L, R, H).transpose(1, 2) for t in (q, k, v))
+        ref = (torch.softmax(qf @ kf.mT / H ** 0.5 + mask.float()[:, None], -1) @ vf).transpose(1, 2).reshape(B, L, R * H)
+        d = (y.float() - ref).abs()
+        excess = (d - (MAX_ABS_TOL + ref.abs() * 2.0 ** -10)).max().item()
+        if not (torch.isfinite(y).all().item() and excess <= 0 and torch.equal(y, y2)):
+            failures.append((H, B, R, L, d.max().item(), fa.select_kernel(B, L, R * H, H, has_mask=True)))
+    assert not failures, failures
+
+
 def test_many_batches_and_heads_index_correctly():
     # every (batch, head) pair gets its own inputs; a wrong offset shows as a large error
     q, k, v = make_inputs(5, 200, 7 * 64, 1.0, 77)
