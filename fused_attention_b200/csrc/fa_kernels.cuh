@@ -411,8 +411,9 @@ __device__ __forceinline__ void add_mask_tile_row(float (&s)[kTile], uint32_t sm
             for (int e = 0; e < 4; ++e) {
                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
                 const int i = b * 64 + c * 8 + 2 * e;
-                s[i] = fmaf(f.x, to_score, s[i]);
-                s[i + 1] = fmaf(f.y, to_score, s[i + 1]);
+                // one packed multiply-add for the two scores (the same two roundings as two scalar ones)
+                unpack_f32x2(fma_f32x2(pack_f32x2(f.x, f.y), pack_f32x2(to_score, to_score), pack_f32x2(s[i], s[i + 1])),
+                             s[i], s[i + 1]);
             }
         }
     }
