@@ -49,11 +49,11 @@ L2_POLICY = "inputs rotate over copies that together exceed the 126 MiB L2"
 # capture was taken at; otherwise the line says that the capture is stale.
 NCU_TRAFFIC = {
     "llama7b_prefill": {"bytes": 247.9e6, "profile": "profiles/fa_fwd_pair_llama7b_prefill.md",
-                        "kernel_sha": "7d9d902d6ac6"},
+                        "kernel_sha": "fd38a85980b2"},
     "vit_l16_ragged": {"bytes": 82.8e6, "profile": "profiles/fa_fwd_pipelined_h64_vit_bert.md",
-                       "kernel_sha": "7d9d902d6ac6"},
+                       "kernel_sha": "fd38a85980b2"},
     "bert_base": {"bytes": 19.0e6, "profile": "profiles/fa_fwd_pipelined_h64_vit_bert.md",
-                  "kernel_sha": "7d9d902d6ac6"},
+                  "kernel_sha": "fd38a85980b2"},
 }
 
 

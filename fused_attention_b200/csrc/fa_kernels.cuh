@@ -184,6 +184,9 @@ __device__ __forceinline__ float row_max(const float (&s)[kTile]) {
 // numerator are fp32, and alpha is exactly 1 on most steps, which lets the O rescale be skipped.
 // The final Y = O / l does not depend on which reference was used.
 constexpr float kLazyRescaleLog2 = 8.f;
+// A row sum of P below this proves that no P of the row exceeds 2^kLazyRescaleLog2 (the margin of one covers
+// the error of ex2.approx at the threshold).
+constexpr float kLazyRescaleSum = 255.f;
 __device__ __forceinline__ float update_max(float& m, const float mx, const float c, float& nmc) {
     const float m_new = fmaxf(m, mx);
     const bool keep = (m_new - m) * c <= kLazyRescaleLog2;   // false for the first tile (m = -inf)
@@ -1201,18 +1204,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 if (ragged) mask_tail(s, static_cast<int>(p.L - j * kTile));
                 if (first) m = row_max(s);   // first key tile of the segment: the reference is its row maximum
-                // Exponentials against the standing reference, with the maximum of the scores taken
-                // in the same pass.  The reference only has to move when a score exceeds it by more
-                // than 2^8 in the exp2 domain.  P has one buffer per tile and the previous step's P V
-                // may still be reading it: the first chunks' exponentials go to registers meanwhile.
+                // Exponentials against the standing reference.  The reference only has to move when a score
+                // exceeds it by more than 2^8 in the exp2 domain.  P has one buffer per tile and the previous
+                // step's P V may still be reading it: the first chunks' exponentials go to registers meanwhile.
                 {
                     // A row that has seen nothing but -inf so far (possible only with a mask) takes 0 as
                     // the reference of its exponents, so that P = 0 and l = 0 instead of inf - inf.
                     float nmc = -m * c;
                     if constexpr (kHasMask) nmc = (m == -INFINITY) ? 0.f : nmc;
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    float mx4[4];   // (not used: the row maximum is only taken when the row sum asks for it)
                     uint32_t held[16 * (C::kHeldChunks > 0 ? C::kHeldChunks : 1)];
-                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, nmc, tP, mx4, held);
+                    float sum = exp_chunks<0, C::kHeldChunks, false, false>(s, c, nmc, tP, mx4, held);
                     if constexpr (C::kHeldChunks > 0) {
                         if (g > 0) {
                             mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
@@ -1221,9 +1223,17 @@ fa_fwd_pipelined(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
 #pragma unroll
                     for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
-                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, nmc, tP, mx4);
-                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                    const bool moved = (mx - m) * c > kLazyRescaleLog2;
+                    sum += exp_chunks<C::kHeldChunks, 4, false>(s, c, nmc, tP, mx4);
+                    // The reference has to move when a score exceeds it by more than 2^8 in the exp2 domain, that is
+                    // when a P exceeds 2^8.  No P can while the row's sum of P stays below 2^8, so the row maximum is
+                    // only taken in a warp where some row's sum says it might (the same decisions as testing every
+                    // row's maximum, which is what costs 64 instructions per row and step).
+                    float mx = m;
+                    bool moved = false;
+                    if (__any_sync(0xffffffffu, sum > kLazyRescaleSum)) {
+                        mx = row_max(s);
+                        moved = (mx - m) * c > kLazyRescaleLog2;
+                    }
                     if (__any_sync(0xffffffffu, moved)) {
                         // Some row of this warp needs a new reference: redo the warp's exponentials
                         // (rows that keep theirs reproduce the same P) and rescale O by alpha; the

@@ -224,9 +224,9 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     // reference of its exponents, so that P = 0 and l = 0 instead of inf - inf.
                     float nmc = -m * c;
                     if constexpr (kHasMask) nmc = (m == -INFINITY) ? 0.f : nmc;
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    float mx4[4];   // (not used: the row maximum is only taken when the row sum asks for it)
                     uint32_t held[16 * C::kHeldChunks];
-                    float sum = exp_chunks<0, C::kHeldChunks, true, false>(s, c, nmc, tP, mx4, held);
+                    float sum = exp_chunks<0, C::kHeldChunks, false, false>(s, c, nmc, tP, mx4, held);
                     if ((warp & 3u) == 0u) FA_STAMP(i, g, 3);
                     if (g > 0) {
                         mbar_wait(bar(BAR_PV0 + i), (g - 1u) & 1u, ctl, kRoleSoftmax | (BAR_PV0 + i));
@@ -235,10 +235,18 @@ fa_fwd_pair(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     if ((warp & 3u) == 0u) FA_STAMP(i, g, 4);
 #pragma unroll
                     for (int ch = 0; ch < C::kHeldChunks; ++ch) tmem_st16(tP + ch * 16, held + ch * 16);
-                    sum += exp_chunks<C::kHeldChunks, 4, true>(s, c, nmc, tP, mx4);
+                    sum += exp_chunks<C::kHeldChunks, 4, false>(s, c, nmc, tP, mx4);
                     if ((warp & 3u) == 0u) FA_STAMP(i, g, 5);
-                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                    const bool moved = (mx - m) * c > kLazyRescaleLog2;
+                    // The reference has to move when a score exceeds it by more than 2^8 in the exp2 domain, that is
+                    // when a P exceeds 2^8.  No P can while the row's sum of P stays below 2^8, so the row maximum is
+                    // only taken in a warp where some row's sum says it might (the same decisions as testing every
+                    // row's maximum, which is what costs 64 instructions per row and step).
+                    float mx = m;
+                    bool moved = false;
+                    if (__any_sync(0xffffffffu, sum > kLazyRescaleSum)) {
+                        mx = row_max(s);
+                        moved = (mx - m) * c > kLazyRescaleLog2;
+                    }
                     if (__any_sync(0xffffffffu, moved)) {
                         const float m_new = moved ? mx : m;
                         const float alpha = moved ? ex2_approx((m - m_new) * c) : 1.f;
